@@ -1,6 +1,7 @@
 from .base import (ConfigError, LayerSpec, ModelConfig, ModelSpec, PartSpec, ScheduleEntry,
                    read_config_json)
+from .kolorax import KoloraxConfig
 from .qwen3 import Qwen3Config
 
 __all__ = ["ConfigError", "LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry",
-           "Qwen3Config", "read_config_json"]
+           "KoloraxConfig", "Qwen3Config", "read_config_json"]

@@ -119,13 +119,16 @@ class LayerSpec:
     """A block: which arrangement joins the parts, and the parts themselves.
 
     ``position`` is the position encoding the mixer applies (rotary) or None.
+    ``feed_forward`` None: the block has a mixer only (and one norm less).
+    ``params``: constants of the arrangement itself (a multiplier on what the parts add).
     """
 
     arrangement: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norms: Tuple[PartSpec, ...]
     position: Optional[PartSpec] = None
+    params: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -138,11 +141,14 @@ class ScheduleEntry:
                caches.  Pointing it at an earlier entry's slot makes this run
                read that entry's cache.
     ``write_cache``  False when the run only reads the (other layer's) cache.
+    ``junction``     (index into ``ModelSpec.junctions``, turn) of a junction part that runs right
+               before this run (the head of a pass over a looped range of layers), or None.
     """
 
     layer: int
     cache: Optional[int] = None
     write_cache: bool = True
+    junction: Optional[Tuple[int, int]] = None
 
 
 @dataclass(frozen=True)
@@ -157,6 +163,17 @@ class ModelSpec:
     head: PartSpec
     # position encoding applied to the embedding output (learned / absolute), or None
     embedding_position: Optional[PartSpec] = None
+    # parts that run between layer runs where a schedule entry names them
+    junctions: Tuple[PartSpec, ...] = ()
+
+    def resolved_junctions(self) -> List[Optional[Tuple[int, int]]]:
+        """Per run of the schedule: (junction, turn) that runs in front of it, or None."""
+        out = []
+        for pos, e in enumerate(self.schedule):
+            if e.junction is not None and not (0 <= e.junction[0] < len(self.junctions)):
+                raise ConfigError(f"schedule[{pos}] names junction {e.junction[0]}, model has {len(self.junctions)}")
+            out.append(None if e.junction is None else (int(e.junction[0]), int(e.junction[1])))
+        return out
 
     def resolved_schedule(self) -> List[Tuple[int, int, bool]]:
         """(layer, cache slot, write) for every run, with defaults filled in,

@@ -12,7 +12,7 @@ namespace ff {
 // ---------------------------------------------------------------- embedding --
 template <typename TT>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TT* __restrict__ table,
-                                 float* __restrict__ out, int H, int V, int* __restrict__ status) {
+                                 float* __restrict__ out, int H, int V, float scale, int* __restrict__ status) {
     pdl_prologue();
     const int t = blockIdx.x;
     int id = ids[t];
@@ -22,7 +22,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const TT* __restri
     }
     const TT* src = table + (size_t)id * H;
     float* dst = out + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]) * scale;
 }
 
 // ------------------------------------------------------ residual add + norm --
@@ -221,13 +221,13 @@ FF_EXPORT int ff_scatter_int(int* buf, const int* upd, int cap, int len, cudaStr
     return 0;
 }
 FF_EXPORT int ff_embedding(const int* ids, const void* table, int table_dtype, float* out, int T,
-                           int H, int V, int* status, cudaStream_t stream) {
+                           int H, int V, float scale, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
     if (table_dtype == 0)
-        FF_LAUNCH((embedding_kernel<float>), T, threads, 0, stream, ids, (const float*)table, out, H, V, status);
+        FF_LAUNCH((embedding_kernel<float>), T, threads, 0, stream, ids, (const float*)table, out, H, V, scale, status);
     else if (table_dtype == 1)
-        FF_LAUNCH((embedding_kernel<bf16>), T, threads, 0, stream, ids, (const bf16*)table, out, H, V, status);
+        FF_LAUNCH((embedding_kernel<bf16>), T, threads, 0, stream, ids, (const bf16*)table, out, H, V, scale, status);
     else
         return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();

@@ -1,0 +1,302 @@
+// Routed experts: the router's choice, the plan that sorts a step's tokens by expert, the
+// grouped products over the experts' stacked matrices, and the weighted sum back into the
+// 32-bit residual.  Nothing here is read by the host: counts, offsets and the list of row
+// tiles stay on the device, and the grouped products are launched for the largest number of
+// tiles a step of that many tokens can have (blocks past the real count leave at once), so a
+// step with routed experts can be captured into a CUDA graph.
+//
+//   s = softmax(z) over all experts (32-bit).  Experts form `groups` equal groups of
+//   neighbours; a group's score is its largest s; only experts of the `keep` best groups may
+//   be chosen; of those the `top` with the largest s are; weights = s / (sum of chosen s + 1e-20).
+//   expert(h) = W_down (g * sigmoid(1.702 g) * (u + 1)),  g = min(W_gate h, limit),
+//   u = clamp(W_up h, -limit, limit).
+//
+// A row of a grouped product is one (token, choice) pair; its result is a plain dot product
+// per output in a fixed order over K, so it does not depend on which other rows share its tile.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace ff {
+
+constexpr int MOE_BM = 64, MOE_BN = 64, MOE_BK = 16;
+
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
+
+// (value, index) arg-max over a warp; the lowest index wins ties
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+}
+
+// One warp per token.
+__global__ void moe_route_kernel(const float* __restrict__ z, int T, int E, int top, int groups, int keep,
+                                 int* __restrict__ ids, float* __restrict__ wts) {
+    pdl_prologue();
+    extern __shared__ float sh[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    float* s = sh + (size_t)warp * (2 * E + groups);
+    float* a = s + E;
+    float* gs = a + E;
+    const float* zr = z + (size_t)t * E;
+    float mx = -CUDART_INF_F;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(zr[e] - mx); s[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+    __syncwarp();
+    const int per = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+        float m = -1.f;
+        for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, s[e]);
+        gs[g] = m;
+    }
+    for (int e = lane; e < E; e += 32) a[e] = -1.f;
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {
+        float bv = -2.f;
+        int bi = 0x7fffffff;
+        for (int g = lane; g < groups; g += 32)
+            if (gs[g] > bv) { bv = gs[g]; bi = g; }
+        warp_argmax(bv, bi);
+        for (int e = bi * per + lane; e < (bi + 1) * per; e += 32) a[e] = s[e];
+        if (lane == 0) gs[bi] = -3.f;
+        __syncwarp();
+    }
+    float total = 0.f;
+    float mine_w = 0.f;
+    int mine_id = 0;
+    for (int k = 0; k < top; ++k) {
+        float bv = -2.f;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (a[e] > bv) { bv = a[e]; bi = e; }
+        warp_argmax(bv, bi);
+        total += bv;
+        if (lane == (k & 31)) {
+            if (k < 32) { mine_w = bv; mine_id = bi; }
+        }
+        if (k >= 32 && lane == 0) { ids[(size_t)t * top + k] = bi; wts[(size_t)t * top + k] = bv; }
+        if (lane == 0) a[bi] = -4.f;
+        __syncwarp();
+    }
+    const float inv = 1.0f / (total + 1e-20f);
+    if (lane < top && lane < 32) {
+        ids[(size_t)t * top + lane] = mine_id;
+        wts[(size_t)t * top + lane] = mine_w * inv;
+    }
+    if (top > 32 && lane == 0)
+        for (int k = 32; k < top; ++k) wts[(size_t)t * top + k] *= inv;
+}
+
+// One block: rows sorted by expert.  seg[e] .. seg[e+1] are expert e's rows; row_of[entry] is
+// the row of (token, choice) = entry; src_tok[row] its token; the row tiles of MOE_BM rows
+// are listed as (expert, first row) with their count in n_tiles.
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int entries, int top, int E, int* __restrict__ seg,
+                                int* __restrict__ row_of, int* __restrict__ src_tok, int* __restrict__ tile_expert,
+                                int* __restrict__ tile_row0, int* __restrict__ n_tiles) {
+    pdl_prologue();
+    extern __shared__ int shi[];
+    int* counts = shi;
+    int* offs = shi + E;
+    int* cursor = offs + E + 1;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < entries; i += blockDim.x) atomicAdd(&counts[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0, nt = 0;
+        for (int e = 0; e < E; ++e) {
+            offs[e] = run;
+            seg[e] = run;
+            for (int r0 = 0; r0 < counts[e]; r0 += MOE_BM) {
+                tile_expert[nt] = e;
+                tile_row0[nt] = run + r0;
+                ++nt;
+            }
+            run += counts[e];
+        }
+        offs[E] = run;
+        seg[E] = run;
+        n_tiles[0] = nt;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+        const int e = ids[i];
+        const int row = offs[e] + atomicAdd(&cursor[e], 1);
+        row_of[i] = row;
+        src_tok[row] = i / top;
+    }
+}
+
+// out rows = A rows x B[e]^T for the row tile's expert e.  B: [E, N, K] row-major.
+// GATEUP: two B matrices (gate and up, [E, N, K] each), A rows gathered from x by src_tok, and
+// out[row, n] = clamped_glu(gate, up) in type T.  Else: A = rows of `a` in place, out 32-bit.
+template <typename T, bool GATEUP>
+__global__ void __launch_bounds__(256) moe_grouped_kernel(
+    const T* __restrict__ a, const int* __restrict__ src_tok, const T* __restrict__ b0, const T* __restrict__ b1,
+    const int* __restrict__ seg, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+    const int* __restrict__ n_tiles, void* __restrict__ out, int N, int K, float limit) {
+    pdl_prologue();
+    if ((int)blockIdx.y >= n_tiles[0]) return;
+    __shared__ float As[MOE_BK][MOE_BM + 1];
+    __shared__ float Bs[GATEUP ? 2 : 1][MOE_BK][MOE_BN + 1];
+    __shared__ int s_src[MOE_BM];
+    const int e = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y];
+    const int rows = min(MOE_BM, seg[e + 1] - row0);
+    const int n0 = blockIdx.x * MOE_BN;
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    if (tid < MOE_BM) s_src[tid] = tid < rows ? (GATEUP ? src_tok[row0 + tid] : row0 + tid) : -1;
+    __syncthreads();
+    const T* B0 = b0 + (size_t)e * N * K;
+    const T* B1 = GATEUP ? b1 + (size_t)e * N * K : nullptr;
+    float acc0[4][4] = {}, acc1[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+        for (int idx = tid; idx < MOE_BM * MOE_BK; idx += 256) {
+            const int r = idx / MOE_BK, kk = idx - r * MOE_BK;
+            const int src = s_src[r];
+            As[kk][r] = (src >= 0 && k0 + kk < K) ? to_float(a[(size_t)src * K + k0 + kk]) : 0.f;
+        }
+        for (int idx = tid; idx < MOE_BN * MOE_BK; idx += 256) {
+            const int n = idx / MOE_BK, kk = idx - n * MOE_BK;
+            const bool ok = n0 + n < N && k0 + kk < K;
+            Bs[0][kk][n] = ok ? to_float(B0[(size_t)(n0 + n) * K + k0 + kk]) : 0.f;
+            if (GATEUP) Bs[1][kk][n] = ok ? to_float(B1[(size_t)(n0 + n) * K + k0 + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; ++kk) {
+            float av[4], bv[4], cv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { bv[j] = Bs[0][kk][tx * 4 + j]; if (GATEUP) cv[j] = Bs[1][kk][tx * 4 + j]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc0[i][j] += av[i] * bv[j];
+                    if (GATEUP) acc1[i][j] += av[i] * cv[j];
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            if (GATEUP) ((T*)out)[(size_t)(row0 + r) * N + n] = from_float<T>(clamped_glu(acc0[i][j], acc1[i][j], limit));
+            else ((float*)out)[(size_t)(row0 + r) * N + n] = acc0[i][j];
+        }
+    }
+}
+
+// y[t, f] = clamped_glu(gu[t, f], gu[t, F + f])
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, int F, float limit, size_t total) {
+    pdl_prologue();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / F;
+    const int f = (int)(idx - t * F);
+    y[idx] = from_float<T>(clamped_glu(to_float(gu[t * 2 * F + f]), to_float(gu[t * 2 * F + F + f]), limit));
+}
+
+// residual[t,:] += mult * (sum_k wts[t,k] * rows[row_of[t*top+k],:] + shared[t,:])
+__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ rows,
+                                   const int* __restrict__ row_of, const float* __restrict__ wts,
+                                   const float* __restrict__ shared, float mult, int top, int W) {
+    pdl_prologue();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k)
+            acc += wts[(size_t)t * top + k] * rows[(size_t)row_of[(size_t)t * top + k] * W + i];
+        if (shared) acc += shared[(size_t)t * W + i];
+        residual[(size_t)t * W + i] += mult * acc;
+    }
+}
+
+}  // namespace ff
+
+using namespace ff;
+
+FF_EXPORT int ff_moe_row_tile() { return MOE_BM; }
+
+FF_EXPORT int ff_moe_route(const float* z, int T, int E, int top, int groups, int keep, int* ids, float* wts,
+                           cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
+        top > keep * (E / groups))
+        return FF_ERR_BAD_ARG;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * (2 * E + groups) * sizeof(float);
+    if (smem > 48 * 1024) return FF_ERR_UNSUPPORTED;
+    FF_LAUNCH(moe_route_kernel, (T + warps - 1) / warps, warps * 32, smem, stream, z, T, E, top, groups, keep, ids, wts);
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_moe_plan(const int* ids, int entries, int top, int E, int* seg, int* row_of, int* src_tok,
+                          int* tile_expert, int* tile_row0, int* n_tiles, cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
+    if (smem > 48 * 1024) return FF_ERR_UNSUPPORTED;
+    FF_LAUNCH(moe_plan_kernel, 1, 1024, smem, stream, ids, entries, top, E, seg, row_of, src_tok, tile_expert, tile_row0,
+              n_tiles);
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_moe_grouped(const void* a, const int* src_tok, const void* b0, const void* b1, int dtype, int gateup,
+                             const int* seg, const int* tile_expert, const int* tile_row0, const int* n_tiles,
+                             void* out, int max_tiles, int N, int K, float limit, cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
+#define FF_MOE(T, G)                                                                                               \
+    FF_LAUNCH((moe_grouped_kernel<T, G>), grid, 256, 0, stream, (const T*)a, src_tok, (const T*)b0, (const T*)b1, seg, \
+              tile_expert, tile_row0, n_tiles, out, N, K, limit)
+    if (dtype == 0 && gateup) FF_MOE(float, true);
+    else if (dtype == 0) FF_MOE(float, false);
+    else if (dtype == 1 && gateup) FF_MOE(bf16, true);
+    else if (dtype == 1) FF_MOE(bf16, false);
+    else return FF_ERR_BAD_ARG;
+#undef FF_MOE
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_clamped_glu(const void* gu, void* y, int dtype, int T, int F, float limit, cudaStream_t stream) {
+    const size_t total = (size_t)T * F;
+    if (total == 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == 0) FF_LAUNCH((clamped_glu_kernel<float>), blocks, 256, 0, stream, (const float*)gu, (float*)y, F, limit, total);
+    else if (dtype == 1) FF_LAUNCH((clamped_glu_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gu, (bf16*)y, F, limit, total);
+    else return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_moe_combine(float* residual, const float* rows, const int* row_of, const float* wts,
+                             const float* shared, float mult, int T, int top, int W, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    FF_LAUNCH(moe_combine_kernel, T, W >= 1024 ? 256 : 128, 0, stream, residual, rows, row_of, wts, shared, mult, top, W);
+    FF_LAUNCH_CHECK();
+    return 0;
+}

@@ -38,23 +38,25 @@ def require_cuda(device) -> torch.device:
 
 
 def load_config_with_file_hints(model_dir: str) -> ModelConfig:
-    """The typed configuration of a model folder.  A config.json that says nothing about
+    """The typed configuration of a model folder.  Sizes that only tensor shapes give are filled in where
+    the design asks for it (``register_architecture(file_hints=)``).  A config.json that says nothing about
     ``tie_word_embeddings`` is read as tied when the weight file holds no ``lm_head.weight``
     (checkpoints with a shared head usually store the matrix once)."""
     from ..config.base import read_config_json
-    from ..models.registry import config_from_dict
+    from ..models.registry import apply_file_hints, architecture_of, config_from_dict
     from ..weights.safetensors_io import open_model_files
     raw = read_config_json(model_dir)
-    if "tie_word_embeddings" not in raw:
-        files = open_model_files(model_dir)
-        try:
-            names = {n for f in files for n in f.entries}
-        finally:
-            for f in files:
-                f.close()
-        if "lm_head.weight" not in names and "model.embed_tokens.weight" in names:
+    architecture_of(raw)                          # an unnamed design is told before the files are opened
+    files = open_model_files(model_dir)
+    try:
+        shapes = {n: tuple(e.shape) for f in files for n, e in f.entries.items()}
+    finally:
+        for f in files:
+            f.close()
+    if "architectures" in raw and "tie_word_embeddings" not in raw:
+        if "lm_head.weight" not in shapes and "model.embed_tokens.weight" in shapes:
             raw = dict(raw, tie_word_embeddings=True)
-    return config_from_dict(raw)
+    return config_from_dict(apply_file_hints(raw, shapes))
 
 
 def load_model(model_dir: str, *, dtype="bfloat16", device="cuda:0", weight_dtype: str = "keep"

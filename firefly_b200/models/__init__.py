@@ -1,4 +1,4 @@
-from . import qwen3  # noqa: F401  (registers Qwen3ForCausalLM)
+from . import kolorax, qwen3  # noqa: F401  (register Kolorax and Qwen3ForCausalLM)
 from .decoder import DecoderModel, expected_weights
 from .registry import (architecture_of, config_from_dict, known_architectures, load_config,
                        register_architecture, spec_for)

@@ -27,16 +27,22 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
         self.schedule = spec.resolved_schedule()
+        # parts that run between two layer runs (the head of a pass over a looped range of layers)
+        self.junctions = [build_part("junction", j, rt) for j in spec.junctions]
+        self.run_junctions = spec.resolved_junctions()
+        self.keeps_embedding_output = any(getattr(j, "needs_embedding_output", False) for j in self.junctions)
         self._takes_next_norm = [declared(b, "takes_next_norm") for b in self.blocks]
         # a part that reads device values on the host keeps the whole model's steps out of CUDA graphs
         self.host_synchronous = any(host_synchronous(p) for p in (
-            self.embedding, self.embedding_position, *self.blocks, self.final_norm, self.head) if p is not None)
+            self.embedding, self.embedding_position, *self.blocks, *self.junctions, self.final_norm, self.head)
+            if p is not None)
         self.bound = False
+        self.after_run = None       # debugging: called as after_run(run index, residual, pending) behind every layer run
 
     # -- weights ------------------------------------------------------------------
     def weight_specs(self) -> List[WeightSpec]:
         seen: Dict[str, WeightSpec] = {}
-        parts = [self.embedding, *self.blocks, self.final_norm, self.head]
+        parts = [self.embedding, *self.blocks, *self.junctions, self.final_norm, self.head]
         if self.embedding_position is not None:
             parts.append(self.embedding_position)
         for p in parts:
@@ -48,7 +54,7 @@ class DecoderModel:
 
     def fused_specs(self, dtype_of) -> list:
         """The fused tensors the parts want (``Part.fused_layout``), each once."""
-        parts = [self.embedding, *self.blocks, self.final_norm, self.head]
+        parts = [self.embedding, *self.blocks, *self.junctions, self.final_norm, self.head]
         if self.embedding_position is not None:
             parts.append(self.embedding_position)
         seen = {}
@@ -63,6 +69,8 @@ class DecoderModel:
             self.embedding_position.bind(tensors)
         for b in self.blocks:
             b.bind(tensors)
+        for j in self.junctions:
+            j.bind(tensors)
         self.final_norm.bind(tensors)
         self.head.bind(tensors)
         self.bound = True
@@ -91,9 +99,17 @@ class DecoderModel:
         if self.embedding_position is not None:
             self.embedding_position.apply_to_embedding(residual, ctx)
         pending: Optional[torch.Tensor] = None
+        stream0 = None
+        if self.keeps_embedding_output:
+            # the embedding output as a junction will want it (the stream itself is updated in place)
+            stream0 = ctx.workspace.get("residual.first", tuple(residual.shape), torch.float32)
+            stream0.copy_(residual)
         runs = self.schedule
         for i, (layer, slot, write) in enumerate(runs):
             block = self.blocks[layer]
+            if self.run_junctions[i] is not None:
+                j, turn = self.run_junctions[i]
+                residual, pending = self.junctions[j].forward(residual, pending, ctx, stream0, turn)
             # the norm that follows this run, for a last product that can fold it in
             nxt = self.blocks[runs[i + 1][0]] if i + 1 < len(runs) else None
             if self._takes_next_norm[layer]:
@@ -101,6 +117,8 @@ class DecoderModel:
                 residual, pending = block.forward(residual, pending, ctx, slot, write, next_norm=next_norm)
             else:
                 residual, pending = block.forward(residual, pending, ctx, slot, write)
+            if self.after_run is not None:
+                self.after_run(i, residual, pending)
         x = self.final_norm.forward(residual, pending, ctx, tag="final_normed", row_idx=ctx.logits_rows)
         return self.head.forward(x, ctx)
 

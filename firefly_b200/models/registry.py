@@ -15,14 +15,27 @@ from typing import Any, Callable, Dict, Mapping, Tuple, Type
 from ..config.base import ConfigError, ModelConfig, ModelSpec, read_config_json
 
 _ARCHITECTURES: Dict[str, Tuple[Type[ModelConfig], Callable[[ModelConfig], ModelSpec]]] = {}
+_FILE_HINTS: Dict[str, Callable[[Mapping[str, Any], Mapping[str, tuple]], Mapping[str, Any]]] = {}
 
 
 def register_architecture(name: str, config_cls: Type[ModelConfig],
                           spec_builder: Callable[[ModelConfig], ModelSpec], *,
-                          replace: bool = False) -> None:
+                          replace: bool = False, file_hints=None) -> None:
+    """``file_hints(raw config, {tensor name: shape}) -> raw config``: for a design some of whose sizes only
+    the checkpoint's tensor shapes give; applied when a model folder is loaded."""
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture '{name}' is already registered")
     _ARCHITECTURES[name] = (config_cls, spec_builder)
+    if file_hints is not None:
+        _FILE_HINTS[name] = file_hints
+    else:
+        _FILE_HINTS.pop(name, None)
+
+
+def apply_file_hints(raw: Mapping[str, Any], shapes: Mapping[str, tuple]) -> Mapping[str, Any]:
+    """``raw`` completed from the tensor shapes of its model folder, if its architecture asks for that."""
+    hint = _FILE_HINTS.get(architecture_of(raw))
+    return hint(raw, shapes) if hint is not None else raw
 
 
 def known_architectures():
@@ -38,9 +51,13 @@ def _entry(name: str):
 
 
 def architecture_of(raw: Mapping[str, Any]) -> str:
+    """The design's name: ``architectures[0]``, or the single name under ``architecture``."""
+    if "architectures" not in raw and isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
     archs = raw.get("architectures")
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
     return archs[0]
 
 

@@ -78,6 +78,10 @@ _MODULES = {
     "gemm_tcgen05": ("gemm_tcgen05.cu", None),
     "gemm_pair": ("gemm_pair.cu", None),
     "weights": ("weights.cu", None),
+    "layer_norm": ("layer_norm.cu", None),
+    "wkv": ("wkv.cu", None),
+    "latent_attention": ("latent_attention.cu", None),
+    "moe": ("moe.cu", None),
 }
 
 
@@ -116,15 +120,16 @@ def build_all(head_dims=DEFAULT_HEAD_DIMS) -> None:
 
 
 # --------------------------------------------------------------------------- #
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out[t,:] = float(table[ids[t],:]); ids int32 [T], out float32 [T,H]."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+              scale: float = 1.0) -> None:
+    """out[t,:] = float(table[ids[t],:]) * scale; ids int32 [T], out float32 [T,H]."""
     _need_cuda(ids, table, out, status)
     assert ids.dtype == torch.int32 and out.dtype == torch.float32
     T, H = out.shape
     V = table.shape[0]
     assert table.shape[1] == H and ids.numel() == T
     _check(_lib("elementwise").ff_embedding(_p(ids), _p(table), c_int(_dt(table)), _p(out), c_int(T),
-                                           c_int(H), c_int(V), _p(status), _stream()), "embedding")
+                                           c_int(H), c_int(V), c_float(scale), _p(status), _stream()), "embedding")
 
 
 def scatter_int(buf: torch.Tensor, updates: torch.Tensor, cap: int) -> None:
@@ -710,3 +715,216 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
             tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
             attn_tiled(q, q_stride, pages, table_t, cu_q_t, ctx_lens_t, n - n_dec,
                        tiles, out, nq, nkv, d, scale, window, ctx.status)
+
+
+# --------------------------------------------------------------------------- #
+# layer norm and the row kernels at the head of a pass of a looped range of layers
+def add_layer_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                   bias: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+                   row_idx: Optional[torch.Tensor] = None, delta_scale: float = 1.0) -> None:
+    """residual (+= delta_scale * delta); out = (v - mean) / sqrt(var + eps) * weight + bias over each row v
+    of the residual (float32 [T,H]).  With ``row_idx`` only those rows, and the residual is not written."""
+    _need_cuda(residual, delta, weight, bias, out, row_idx)
+    assert residual.dtype == torch.float32 and weight.dtype == torch.float32
+    H = residual.shape[-1]
+    rows = out.shape[0]
+    assert out.shape[-1] == H and weight.numel() == H and (bias is None or (bias.numel() == H and bias.dtype == torch.float32))
+    if row_idx is None:
+        assert rows == residual.shape[0]
+    else:
+        assert row_idx.dtype == torch.int32 and row_idx.numel() == rows
+    if delta is not None:
+        assert delta.shape == residual.shape
+    _check(_lib("layer_norm").ff_add_layer_norm(
+        _p(residual), _p(delta), c_int(_dt(delta) if delta is not None else 0), c_float(delta_scale), _p(row_idx),
+        _p(weight), _p(bias), c_float(eps), _p(out), c_int(_dt(out)), c_int(rows), c_int(H),
+        c_int(1 if row_idx is None else 0), _stream()), "add_layer_norm")
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t] | b[t]] for two float32 [T,H] streams, in out's type [T,2H]."""
+    _need_cuda(a, b, out)
+    T, H = a.shape
+    assert a.dtype == b.dtype == torch.float32 and b.shape == a.shape and out.shape == (T, 2 * H)
+    _check(_lib("layer_norm").ff_concat_cast(_p(a), _p(b), _p(out), c_int(_dt(out)), c_int(T), c_int(H), _stream()),
+           "concat_cast")
+
+
+def add_row_vector(x: torch.Tensor, v: torch.Tensor, scale: float = 1.0) -> None:
+    """x[t,:] += scale * v for float32 x [T,H], v [H]."""
+    _need_cuda(x, v)
+    assert x.dtype == v.dtype == torch.float32 and v.numel() == x.shape[1]
+    _check(_lib("layer_norm").ff_add_row_vector(_p(x), _p(v), c_float(scale), c_int(x.shape[0]), c_int(x.shape[1]),
+                                               _stream()), "add_row_vector")
+
+
+def linear_scaled_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, alpha: float) -> None:
+    """residual (float32) += alpha * x @ weight^T through the library, summed in 32-bit."""
+    _need_cuda(x, weight, residual)
+    if x.dtype != weight.dtype or residual.dtype != torch.float32:
+        raise KernelError(f"linear_scaled_add: {x.dtype} x {weight.dtype} into {residual.dtype}")
+    if x.dtype == torch.float32:
+        torch.addmm(residual, x, weight.t(), alpha=alpha, out=residual)
+    else:
+        torch.addmm(residual, x, weight.t(), alpha=alpha, out_dtype=torch.float32, out=residual)
+
+
+def batched_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b] = x[b] @ weight[b]^T for b in a batch (the library's batched product); x [B,T,K] and weight
+    [B,N,K] may be strided views with unit inner stride, out [B,T,N] is contiguous."""
+    if not (x.is_cuda and weight.is_cuda and out.is_cuda):
+        raise KernelError("firefly_b200 kernels run on a CUDA device only")
+    if x.dtype != weight.dtype or out.dtype != x.dtype or not out.is_contiguous():
+        raise KernelError("batched_linear: operands and result share one type; the result is contiguous")
+    torch.bmm(x, weight.transpose(1, 2), out=out)
+
+
+# --------------------------------------------------------------------------- #
+# the recurrent mixer with a matrix state per head (csrc/wkv.cu)
+def wkv_shift_mix(x, mu, state, prev_off: int, ctx, mixes) -> None:
+    """mixes[s, t] = x[t] + (x[t-1] - x[t]) * mu[s] for the five inputs of the mixer; the row in front of a
+    portion's first token comes from the request's state slot (zeros for a fresh request)."""
+    _need_cuda(x, mu, state, mixes)
+    T, W = x.shape
+    assert mu.dtype == torch.float32 and mu.shape == (5, W) and state.dtype == torch.float32 and state.dim() == 2
+    assert mixes.shape == (5, T, W) and mixes.dtype == x.dtype
+    _check(_lib("wkv").ff_wkv_shift_mix(_p(x), c_int(_dt(x)), _p(mu), _p(state), ctypes.c_longlong(state.stride(0)),
+                                       c_int(prev_off), _p(ctx.token_seq), _p(ctx.cu_q), _p(ctx.state_slots),
+                                       _p(ctx.seq_fresh), _p(mixes), c_int(T), c_int(W), _stream()), "wkv_shift_mix")
+
+
+def tanh_cast(src: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(src, out)
+    assert src.dtype == torch.float32 and src.numel() == out.numel()
+    _check(_lib("wkv").ff_tanh_cast(_p(src), _p(out), c_int(_dt(out)), ctypes.c_longlong(src.numel()), _stream()),
+           "tanh_cast")
+
+
+WKV_MAX_DIM = 128
+
+
+def wkv_scan(rkvg, dlog, w0, u, state, prev_off: int, x, ctx, o, heads: int, dim: int) -> None:
+    """The recurrence, token by token, one block per (sequence, head).  rkvg [4,T,heads*dim] (r, k, v, gate
+    projections; the gate is not read here), dlog float32 [T,heads*dim] (the decay's inner logarithm without
+    its offset w0), state float32 [slots, heads*dim*dim + W] (read unless the request is fresh, written back,
+    and the portion's last row of x saved behind it), o float32 [T, heads*dim]."""
+    _need_cuda(rkvg, dlog, w0, u, state, x, o)
+    T, W = x.shape
+    HD = heads * dim
+    assert rkvg.shape == (4, T, HD) and rkvg.dtype == x.dtype and dlog.shape == (T, HD) and dlog.dtype == torch.float32
+    assert o.shape == (T, HD) and o.dtype == torch.float32 and state.dtype == torch.float32
+    assert w0.dtype == u.dtype == torch.float32 and w0.numel() == HD and u.numel() == HD
+    assert state.shape[1] >= prev_off + W and prev_off >= heads * dim * dim
+    _check(_lib("wkv").ff_wkv_scan(_p(rkvg), c_int(_dt(rkvg)), _p(dlog), _p(w0), _p(u), _p(state),
+                                  ctypes.c_longlong(state.stride(0)), c_int(prev_off), _p(x), c_int(W), _p(ctx.cu_q),
+                                  _p(ctx.state_slots), _p(ctx.seq_fresh), _p(o), c_int(T), c_int(ctx.num_seqs),
+                                  c_int(heads), c_int(dim), _stream()), "wkv_scan")
+
+
+def wkv_out(o, gate, norm_w, eps: float, y, heads: int, dim: int) -> None:
+    """y = o / rms(o over a head) * norm_w * silu(gate); o float32 [T, heads*dim], gate and y in the activation type."""
+    _need_cuda(o, gate, norm_w, y)
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and norm_w.dtype == torch.float32 and gate.dtype == y.dtype
+    assert gate.shape == o.shape == y.shape and o.shape[1] == heads * dim
+    _check(_lib("wkv").ff_wkv_out(_p(o), _p(gate), c_int(_dt(gate)), _p(norm_w), c_float(eps), _p(y), c_int(T),
+                                 c_int(heads), c_int(dim), _stream()), "wkv_out")
+
+
+# --------------------------------------------------------------------------- #
+# attention over a cached latent vector (csrc/latent_attention.cu)
+def latent_finish(proj, q_off: int, dkv_off: int, q_abs, c_norm_w, eps: float, freq, ctx, table, pages, q_full,
+                  heads: int, dim: int, rot: int, kv_rank: int) -> None:
+    """Finish a step's query rows and write its cache rows.  proj [T, *] holds the q heads ([heads, dim + rot]
+    from column q_off) and the down projection ([kv_rank + rot] from column dkv_off); q_abs [heads, T, kv_rank];
+    freq float64 [rot/2]; pages [blocks, 2, 1, block, kv_rank + rot]; q_full [T, heads * (kv_rank + rot)]."""
+    _need_cuda(proj, q_abs, c_norm_w, freq, table, pages, q_full)
+    T = proj.shape[0]
+    d = kv_rank + rot
+    num_blocks, two, one, block_size, cd = pages.shape
+    assert two == 2 and one == 1 and cd == d and pages.dtype == proj.dtype == q_abs.dtype == q_full.dtype
+    assert q_abs.shape == (heads, T, kv_rank) and q_full.shape == (T, heads * d)
+    assert freq.dtype == torch.float64 and freq.numel() == rot // 2 and c_norm_w.dtype == torch.float32
+    _check(_lib("latent_attention").ff_latent_finish(
+        _p(proj), c_int(_dt(proj)), c_int(proj.stride(0)), c_int(q_off), c_int(dkv_off), _p(q_abs), _p(c_norm_w),
+        c_float(eps), _p(freq), _p(ctx.positions), _p(ctx.token_seq), _p(table), c_int(table.shape[1]),
+        c_int(block_size), c_int(num_blocks), _p(pages), _p(q_full), c_int(T), c_int(heads), c_int(dim), c_int(rot),
+        c_int(kv_rank), _p(ctx.status), _stream()), "latent_finish")
+
+
+def latent_gate(val, g, y, heads: int, vdim: int) -> None:
+    """y[t, h*vdim + j] = val[h, t, j] * sigmoid(g[t, h*vdim + j]); g may be a column range of a wider matrix."""
+    if not g.is_cuda or g.stride(1) != 1:
+        raise KernelError("latent_gate: the gate must be a CUDA matrix with contiguous rows")
+    _need_cuda(val, y)
+    T = y.shape[0]
+    assert val.shape == (heads, T, vdim) and y.shape == (T, heads * vdim) and val.dtype == g.dtype == y.dtype
+    _check(_lib("latent_attention").ff_latent_gate(_p(val), c_void_p(g.data_ptr()), c_int(g.stride(0)), c_int(_dt(y)),
+                                                  _p(y), c_int(T), c_int(heads), c_int(vdim), _stream()), "latent_gate")
+
+
+# --------------------------------------------------------------------------- #
+# routed experts (csrc/moe.cu)
+@functools.lru_cache(maxsize=None)
+def moe_row_tile() -> int:
+    return int(_lib("moe").ff_moe_row_tile())
+
+
+def moe_route(z, ids, wts, groups: int, keep: int) -> None:
+    """Choice of experts per token from router logits z float32 [T,E]: ids int32 [T,top], wts float32 [T,top]."""
+    _need_cuda(z, ids, wts)
+    T, E = z.shape
+    top = ids.shape[1]
+    assert z.dtype == torch.float32 and ids.dtype == torch.int32 and wts.dtype == torch.float32 and wts.shape == ids.shape
+    _check(_lib("moe").ff_moe_route(_p(z), c_int(T), c_int(E), c_int(top), c_int(groups), c_int(keep), _p(ids), _p(wts),
+                                   _stream()), "moe_route")
+
+
+def moe_plan(ids, E: int, seg, row_of, src_tok, tile_expert, tile_row0, n_tiles) -> None:
+    """Sort the step's (token, choice) pairs by expert, on the device (all int32)."""
+    _need_cuda(ids, seg, row_of, src_tok, tile_expert, tile_row0, n_tiles)
+    T, top = ids.shape
+    assert seg.numel() >= E + 1 and row_of.numel() >= T * top and src_tok.numel() >= T * top
+    assert tile_expert.numel() >= moe_max_tiles(T * top, E) and tile_row0.numel() >= moe_max_tiles(T * top, E)
+    _check(_lib("moe").ff_moe_plan(_p(ids), c_int(T * top), c_int(top), c_int(E), _p(seg), _p(row_of), _p(src_tok),
+                                  _p(tile_expert), _p(tile_row0), _p(n_tiles), _stream()), "moe_plan")
+
+
+def moe_max_tiles(entries: int, E: int) -> int:
+    """The most row tiles `entries` rows spread over E experts can make."""
+    return entries // moe_row_tile() + min(E, entries)
+
+
+def moe_grouped(a, src_tok, b0, b1, plan, out, limit: float = 0.0) -> None:
+    """Grouped product over the experts' stacked matrices.  With ``b1`` (gate|up): rows of ``a`` [T,K] gathered
+    by src_tok, b0/b1 [E,N,K], out[row] = g * sigmoid(1.702 g) * (u + 1) with the clamps of ``limit``, in a's
+    type.  Without: a [rows,K] in place, out float32 [rows,N].  ``plan`` = (seg, tile_expert, tile_row0, n_tiles,
+    max_tiles)."""
+    seg, tile_expert, tile_row0, n_tiles, max_tiles = plan
+    _need_cuda(a, src_tok, b0, b1, out)
+    E, N, Kd = b0.shape
+    assert a.shape[1] == Kd and a.dtype == b0.dtype and out.shape[1] == N
+    assert out.dtype == (a.dtype if b1 is not None else torch.float32)
+    _check(_lib("moe").ff_moe_grouped(_p(a), _p(src_tok), _p(b0), _p(b1), c_int(_dt(a)), c_int(1 if b1 is not None else 0),
+                                     _p(seg), _p(tile_expert), _p(tile_row0), _p(n_tiles), _p(out), c_int(max_tiles),
+                                     c_int(N), c_int(Kd), c_float(limit), _stream()), "moe_grouped")
+
+
+def clamped_glu(gu, y, limit: float) -> None:
+    """y = g * sigmoid(1.702 g) * (u + 1), g = min(gu[:, :F], limit), u = clamp(gu[:, F:], -limit, limit)."""
+    _need_cuda(gu, y)
+    T, F = y.shape
+    assert gu.shape == (T, 2 * F) and gu.dtype == y.dtype
+    _check(_lib("moe").ff_clamped_glu(_p(gu), _p(y), c_int(_dt(y)), c_int(T), c_int(F), c_float(limit), _stream()),
+           "clamped_glu")
+
+
+def moe_combine(residual, rows, row_of, wts, shared, mult: float) -> None:
+    """residual[t] += mult * (sum_k wts[t,k] * rows[row_of[t,k]] + shared[t]); everything float32."""
+    _need_cuda(residual, rows, row_of, wts, shared)
+    T, W = residual.shape
+    top = wts.shape[1]
+    assert residual.dtype == rows.dtype == wts.dtype == torch.float32 and rows.shape[1] == W
+    assert shared is None or (shared.dtype == torch.float32 and shared.shape == residual.shape)
+    _check(_lib("moe").ff_moe_combine(_p(residual), _p(rows), _p(row_of), _p(wts), _p(shared), c_float(mult), c_int(T),
+                                     c_int(top), c_int(W), _stream()), "moe_combine")

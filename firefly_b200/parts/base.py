@@ -19,6 +19,9 @@ Categories and what each must offer (beyond ``weight_specs`` and ``bind``):
                     ``forward(residual, pending, ctx, slot, write_cache)``
                     -> (residual, pending): ``pending`` is a delta that has not
                     been added to the residual yet (the next norm folds it in).
+* ``junction``      runs between two layer runs where the schedule says so (the head of a pass
+                    over a looped range of layers): ``forward(residual, pending, ctx, stream0,
+                    turn) -> (residual, pending)``.
 * ``embedding``     ``forward(ctx) -> residual`` float32 [T, hidden].
 * ``head``          ``forward(x_rows) -> logits`` float32 [rows, vocab].
 
@@ -36,6 +39,8 @@ adds_into_residual      forward(accumulate_into=)   mixer / feed_forward may add
                                                     32-bit residual itself and return None
 folds_next_norm         forward(then_norm=)         ... and, told which norm follows, may leave that
                                                     norm folded (a ``FoldedNorm``) for its consumer
+scales_residual         forward(residual_scale=)    ... and adds it times a constant (a block whose parts'
+                                                    outputs enter the stream times a multiplier)
 accepts_folded_norm     (none)                      its first operation can finish a ``FoldedNorm``
 takes_next_norm         forward(next_norm=)         arrangement: hands the next block's first norm
                                                     to its last part
@@ -60,7 +65,7 @@ import torch
 from ..config.base import ConfigError, PartSpec
 from ..weights.loader import WeightSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "junction")
 _REGISTRY: Dict[str, Dict[str, type]] = {c: {} for c in CATEGORIES}
 
 
@@ -81,7 +86,7 @@ def part_class(category: str, kind: str) -> type:
 
 
 _FLAG_KEYWORD = {"adds_into_residual": "accumulate_into", "folds_next_norm": "then_norm",
-                 "takes_next_norm": "next_norm"}
+                 "takes_next_norm": "next_norm", "scales_residual": "residual_scale"}
 _FLAG_MEMBERS = {"foldable": ("fold_buffers", "size", "eps")}
 
 
@@ -100,8 +105,8 @@ def declared(part, flag: str) -> bool:
     for member in _FLAG_MEMBERS.get(flag, ()):
         if has and not hasattr(part, member):
             raise ConfigError(f"{who} declares {flag} = True but has no '{member}'")
-    if flag == "folds_next_norm" and has and not getattr(part, "adds_into_residual", False):
-        raise ConfigError(f"{who} declares folds_next_norm without adds_into_residual")
+    if flag in ("folds_next_norm", "scales_residual") and has and not getattr(part, "adds_into_residual", False):
+        raise ConfigError(f"{who} declares {flag} without adds_into_residual")
     return has
 
 
@@ -131,6 +136,7 @@ class Part:
 
     # optional abilities (see the module's table); a subclass that has one sets it to True
     adds_into_residual = False
+    scales_residual = False
     folds_next_norm = False
     accepts_folded_norm = False
     foldable = False

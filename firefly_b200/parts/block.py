@@ -26,27 +26,33 @@ class Block:
         self.position = build_part("position", layer_spec.position, rt) \
             if layer_spec.position is not None else None
         self.mixer = build_part("mixer", layer_spec.mixer, rt, position=self.position)
-        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt)
-        if len(layer_spec.norms) != self.n_norms:
-            raise ValueError(f"arrangement '{layer_spec.arrangement}' needs {self.n_norms} norms, "
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt) \
+            if layer_spec.feed_forward is not None else None
+        self.params = dict(getattr(layer_spec, "params", None) or {})
+        want_norms = self.n_norms if self.feed_forward is not None else self.n_norms - 1
+        if len(layer_spec.norms) != want_norms:
+            raise ValueError(f"arrangement '{layer_spec.arrangement}' needs {want_norms} norms, "
                              f"got {len(layer_spec.norms)}")
         self.norms = [build_part("norm", n, rt) for n in layer_spec.norms]
         # the parts' declared abilities (parts/base.py), checked here against their signatures:
         # adding into the 32-bit residual themselves, folding the norm that follows into their last
         # product, taking a folded norm as input
         self._mixer_fuses = declared(self.mixer, "adds_into_residual")
-        self._ffn_fuses = declared(self.feed_forward, "adds_into_residual")
+        has_ffn = self.feed_forward is not None
+        self._ffn_fuses = has_ffn and declared(self.feed_forward, "adds_into_residual")
         self._mixer_folds = declared(self.mixer, "folds_next_norm")
-        self._ffn_folds = declared(self.feed_forward, "folds_next_norm")
+        self._ffn_folds = has_ffn and declared(self.feed_forward, "folds_next_norm")
         self._mixer_defers = declared(self.mixer, "accepts_folded_norm")
-        self._ffn_defers = declared(self.feed_forward, "accepts_folded_norm")
+        self._ffn_defers = has_ffn and declared(self.feed_forward, "accepts_folded_norm")
+        self._mixer_scales = declared(self.mixer, "scales_residual")
+        self._ffn_scales = has_ffn and declared(self.feed_forward, "scales_residual")
         self._norm_folds = [declared(nrm, "foldable") for nrm in self.norms]
         for k, nrm in enumerate(self.norms):
             if self._norm_folds[k]:
                 nrm.fold_tag = f"fold.{k}"      # scratch of the folded form, one per norm of the block
 
     def parts(self) -> List[Part]:
-        out = [self.mixer, self.feed_forward, *self.norms]
+        out = [p for p in (self.mixer, self.feed_forward, *self.norms) if p is not None]
         if self.position is not None:
             out.append(self.position)
         return out
@@ -104,4 +110,42 @@ class PreNormBlock(Block):
         return residual, f
 
 
+class ScaledPreNormBlock(Block):
+    """h += m * mixer(norm_0(h));  h += m * feed_forward(norm_1(h))  with one multiplier m
+    (``params["residual_mult"]``) on everything the parts add; a block without a feed-forward ends
+    after the mixer.  Parts that declare ``scales_residual`` add their scaled output into the 32-bit
+    stream themselves; another part's delta is added times m by the norm that follows (which must
+    take ``delta_scale``) or, at the block's end, in a pass of its own."""
+
+    def __init__(self, layer_spec, rt: Runtime):
+        super().__init__(layer_spec, rt)
+        self.mult = float(self.params.get("residual_mult", 1.0))
+        if self.feed_forward is not None and not getattr(self.norms[1], "takes_delta_scale", False) \
+                and not (self._mixer_fuses and (self._mixer_scales or self.mult == 1.0)):
+            raise ValueError(f"arrangement '{layer_spec.arrangement}': the mixer leaves a delta and the second "
+                             "norm cannot add it times a multiplier")
+
+    def _run(self, part, fuses, scales, residual, *args):
+        if fuses and scales:
+            return part.forward(*args, accumulate_into=residual, residual_scale=self.mult)
+        if fuses and self.mult == 1.0:
+            return part.forward(*args, accumulate_into=residual)
+        return part.forward(*args)
+
+    def forward(self, residual: torch.Tensor, pending, ctx, slot: int, write_cache: bool):
+        x = self.norms[0].forward(residual, pending, ctx)            # a delta handed over by another block is unscaled
+        a = self._run(self.mixer, self._mixer_fuses, self._mixer_scales, residual, x, ctx, slot, write_cache)
+        if self.feed_forward is None:
+            if a is not None:
+                residual.add_(a.to(torch.float32), alpha=self.mult)
+            return residual, None
+        x = self.norms[1].forward(residual, a, ctx, delta_scale=self.mult) if a is not None \
+            else self.norms[1].forward(residual, None, ctx)
+        f = self._run(self.feed_forward, self._ffn_fuses, self._ffn_scales, residual, x, ctx)
+        if f is not None:
+            residual.add_(f.to(torch.float32), alpha=self.mult)
+        return residual, None
+
+
 register_part("arrangement", "pre_norm", PreNormBlock)
+register_part("arrangement", "scaled_pre_norm", ScaledPreNormBlock)

@@ -27,17 +27,19 @@ class TokenEmbedding(Part):
         super().__init__(spec, rt)
         self.vocab = int(self.p("vocab_size"))
         self.hidden = int(self.p("hidden_size"))
+        self.scale = float(self.p("scale", 1.0))                 # the rows enter the stream times this, in 32-bit
+        self.tensor = self.p("tensor", None) or self.name("weight")   # full tensor name, if it is not <prefix>.weight
         self.table = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.name("weight"), (self.vocab, self.hidden))]
+        return [WeightSpec(self.tensor, (self.vocab, self.hidden))]
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.table = self._matrix(tensors[self.name("weight")])
+        self.table = self._matrix(tensors[self.tensor])
 
     def forward(self, ctx) -> torch.Tensor:
         out = ctx.workspace.get("residual", (ctx.num_tokens, self.hidden), torch.float32)
-        K.embedding(ctx.token_ids, self.table, out, ctx.status)
+        K.embedding(ctx.token_ids, self.table, out, ctx.status, self.scale)
         return out
 
 
@@ -47,15 +49,16 @@ class LMHead(Part):
         self.vocab = int(self.p("vocab_size"))
         self.hidden = int(self.p("hidden_size"))
         self.tied_to = self.p("tied_to", None)
+        self.tensor = self.p("tensor", None) or self.name("weight")   # full tensor name, if it is not <prefix>.weight
         self.weight = None
 
     def weight_specs(self) -> List[WeightSpec]:
         # a tied head has no tensor of its own; one stored anyway is ignored
-        return [WeightSpec(self.name("weight"), (self.vocab, self.hidden),
+        return [WeightSpec(self.tensor, (self.vocab, self.hidden),
                            optional=self.tied_to is not None)]
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        src = self.tied_to if self.tied_to is not None else self.name("weight")
+        src = self.tied_to if self.tied_to is not None else self.tensor
         self.weight = self._matrix(tensors[src])
 
     def forward(self, x_rows: torch.Tensor, ctx) -> torch.Tensor:

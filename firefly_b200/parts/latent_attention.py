@@ -1,0 +1,122 @@
+"""Attention whose keys and values are re-made from a small cached latent vector.
+
+Per token the cache holds c [kv_rank] (the first kv_rank outputs of the down projection W_dkv,
+RMS-normed with a plain weight) and k_rot [rot_dim] (its last rot_dim outputs, rotated, one key part
+shared by all heads).  Head h has key [W_uk[h] c | k_rot] and value W_uv[h] c; its query is laid out
+[dim plain | rot_dim rotated]; score = (q_plain . k_plain + q_rot . k_rot) * scale; causal softmax
+over all earlier tokens; the concatenated heads are multiplied by sigmoid(W_g x) and go through W_o.
+
+The products with W_uk and W_uv are moved to the query side:  q_plain . (W_uk[h] c) = (W_uk[h]^T
+q_plain) . c, and sum_j p_j W_uv[h] c_j = W_uv[h] (sum_j p_j c_j).  What remains over the cache is
+attention with one key/value head of size kv_rank + rot_dim whose keys are the cache rows and whose
+values are their first kv_rank elements: the paged attention kernels of the other mixers run it
+(tcgen05 / mma.sync / plain, by size and type), prompts and decoding alike.  The rotation is
+rotate-half over the rot_dim part, angle = position * base^(-2i/rot_dim), formed in double.
+
+Parameters: hidden_size, heads, dim, rot_dim, vdim, kv_rank, scale, eps (of the latent's norm),
+cache_block_size (optional).  Position part: ``rotary`` with head_dim = rotary_dim = rot_dim.
+Tensors: q [heads*(dim+rot_dim), W]; dkv [kv_rank+rot_dim, W]; dkv.norm [kv_rank];
+uk [heads*dim, kv_rank]; uv [heads*vdim, kv_rank]; g [heads*vdim, W]; o [W, heads*vdim].
+"""
+from __future__ import annotations
+
+from typing import List, Mapping
+
+import torch
+
+from ..cache.spec import PagedKVSpec
+from ..ops import kernels as K
+from ..weights.arena import FusedSpec, Piece
+from ..weights.loader import WeightSpec
+from .base import Part, register_part
+from .linear import apply_linear, scaled_linear_into_residual
+
+
+class LatentAttention(Part):
+    adds_into_residual = True        # forward(accumulate_into=...)
+    scales_residual = True           # forward(residual_scale=...)
+
+    def __init__(self, spec, rt, position=None):
+        super().__init__(spec, rt)
+        self.hidden = int(self.p("hidden_size"))
+        self.heads = int(self.p("heads"))
+        self.dim = int(self.p("dim"))
+        self.rot = int(self.p("rot_dim"))
+        self.vdim = int(self.p("vdim"))
+        self.rank = int(self.p("kv_rank"))
+        self.scale = float(self.p("scale"))
+        self.eps = float(self.p("eps"))
+        self.cache_block_size = self.p("cache_block_size", None)
+        self.position = position
+        self.d = self.rank + self.rot                      # size of a cache row and of a finished query head
+        if self.rot % 2:
+            raise ValueError(f"{self.prefix}: rot_dim {self.rot} must be even")
+        if self.rot and (position is None or not hasattr(position, "frequencies")):
+            raise ValueError(f"{self.prefix}: needs a rotary position part")
+        if self.d > 256:
+            raise ValueError(f"{self.prefix}: kv_rank + rot_dim = {self.d} > 256 is not supported by the attention kernels")
+        self.n_q, self.n_dkv, self.n_g = self.heads * (self.dim + self.rot), self.d, self.heads * self.vdim
+        self.w_in = self.w_uk = self.w_uv = self.w_o = self.c_norm = None
+
+    def cache_spec(self):
+        # one key/value head per token; the value plane repeats the latent (the attention kernels read values
+        # from a plane of their own)
+        return PagedKVSpec(1, self.d, None, None if self.cache_block_size is None else int(self.cache_block_size))
+
+    def weight_specs(self) -> List[WeightSpec]:
+        n, W = self.name, self.hidden
+        return [WeightSpec(n("q"), (self.n_q, W)), WeightSpec(n("dkv"), (self.n_dkv, W)),
+                WeightSpec(n("dkv.norm"), (self.rank,), init="norm", as_float32=True),
+                WeightSpec(n("uk"), (self.heads * self.dim, self.rank)),
+                WeightSpec(n("uv"), (self.heads * self.vdim, self.rank)),
+                WeightSpec(n("g"), (self.n_g, W)), WeightSpec(n("o"), (W, self.n_g))]
+
+    def fused_layout(self, dtype_of) -> List[FusedSpec]:
+        """q, the down projection and the gate read the same input: one matrix, their rows in this order."""
+        n = self.name
+        return [FusedSpec(n("q_dkv_g"), (self.n_q + self.n_dkv + self.n_g, self.hidden),
+                          (Piece(n("q"), 0), Piece(n("dkv"), self.n_q), Piece(n("g"), self.n_q + self.n_dkv)))]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self.name
+        if n("q_dkv_g") in tensors:
+            self.w_in = self._matrix(tensors[n("q_dkv_g")])
+        else:
+            mats = [self._matrix(tensors[n(s)]) for s in ("q", "dkv", "g")]
+            if len({m.dtype for m in mats}) != 1:
+                mats = [m.to(torch.float32) for m in mats]
+            self.w_in = torch.cat(mats, dim=0).contiguous()
+        dt = self.w_in.dtype
+        # [heads, kv_rank, dim]: the transposed key up-projection, so that q_abs = q_plain @ it^T
+        self.w_uk = self._matrix(tensors[n("uk")]).to(dt).view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = self._matrix(tensors[n("uv")]).to(dt).view(self.heads, self.vdim, self.rank).contiguous()
+        self.w_o = self._matrix(tensors[n("o")])
+        self.c_norm = self._vector32(tensors[n("dkv.norm")])
+
+    def forward(self, x, ctx, slot: int, write_cache: bool, accumulate_into=None, residual_scale: float = 1.0):
+        if not write_cache:
+            raise RuntimeError(f"{self.prefix}: this mixer writes the cache it reads")
+        T, ws, H, d = x.shape[0], ctx.workspace, self.heads, self.d
+        dt = self.w_in.dtype
+        proj = ws.get("lat.proj", (T, self.n_q + self.n_dkv + self.n_g), dt)
+        apply_linear(x, self.w_in, proj, ctx, "lat.proj")
+        # W_uk[h]^T q_plain[h] for every head: the heads are the batch of one library product
+        q_plain = proj[:, :self.n_q].view(T, H, self.dim + self.rot)[:, :, :self.dim].transpose(0, 1)
+        q_abs = ws.get("lat.q_abs", (H, T, self.rank), dt)
+        K.batched_linear(q_plain, self.w_uk, q_abs)
+        pages, table = ctx.kv(slot)
+        q_full = ws.get("lat.q_full", (T, H * d), dt)
+        freq = self.position.frequencies() if self.rot else torch.empty(0, dtype=torch.float64, device=x.device)
+        K.latent_finish(proj, 0, self.n_q, q_abs, self.c_norm, self.eps, freq, ctx, table, pages, q_full,
+                        H, self.dim, self.rot, self.rank)
+        att = ws.get("lat.att", (T, H * d), dt)
+        K.paged_attention(q_full, H * d, pages, table, ctx, att, H, 1, d, self.scale, 0)
+        latent = att.view(T, H, d)[:, :, :self.rank].transpose(0, 1)
+        val = ws.get("lat.val", (H, T, self.vdim), dt)
+        K.batched_linear(latent, self.w_uv, val)
+        y = ws.get("lat.y", (T, self.n_g), dt)
+        K.latent_gate(val, proj[:, self.n_q + self.n_dkv:], y, H, self.vdim)
+        return scaled_linear_into_residual(y, self.w_o, accumulate_into, residual_scale, ctx, "lat.out")
+
+
+register_part("mixer", "latent_attention", LatentAttention)

@@ -145,3 +145,17 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, inter: int, interlea
     apply_linear(x, w_gate_up, gu, ctx, "mlp.gate_up")
     K.silu_mul(gu, act, interleaved)
     return act
+
+
+def scaled_linear_into_residual(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor], alpha: float,
+                                ctx, tag: str):
+    """residual += alpha * x W^T, summed in 32-bit, and None; or, without a residual (or when the types do
+    not allow the fused sum), the plain product as a delta that the caller adds times ``alpha``.  With
+    ``alpha`` 1 this is `linear_into_residual`; else the library forms the scaled sum."""
+    if residual is not None and alpha == 1.0:
+        return linear_into_residual(x, weight, residual, ctx, tag)
+    if residual is not None and x.dtype == weight.dtype and residual.dtype == torch.float32 and residual.is_contiguous():
+        K.linear_scaled_add(x, weight, residual, alpha)
+        return None
+    out = ctx.workspace.get(tag, (x.shape[0], weight.shape[0]), ctx.dtype)
+    return apply_linear(x, weight, out, ctx, tag)

@@ -70,4 +70,43 @@ class RMSNorm(Part):
         return out
 
 
+class LayerNorm(Part):
+    """y = (x - mean) / sqrt(var + eps) * weight + bias, var the mean of the squared deviations, in 32-bit.
+    Tensors: ``<prefix>`` + ``weight_leaf`` and ``bias_leaf`` (parameters, so that a checkpoint may call them
+    as it likes; ``bias_leaf`` None: no bias).  ``forward`` takes ``delta_scale``: the pending delta is added
+    as ``delta_scale * delta`` (a block whose parts' outputs enter the stream times a constant)."""
+
+    takes_delta_scale = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.size = int(self.p("size"))
+        self.eps = float(self.p("eps"))
+        self.weight_leaf = self.p("weight_leaf", ".weight")
+        self.bias_leaf = self.p("bias_leaf", ".bias")
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        out = [WeightSpec(self.prefix + self.weight_leaf, (self.size,), init="norm", as_float32=True)]
+        if self.bias_leaf is not None:
+            out.append(WeightSpec(self.prefix + self.bias_leaf, (self.size,), init="zeros", as_float32=True))
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.weight = self._vector32(tensors[self.prefix + self.weight_leaf])
+        if self.bias_leaf is not None:
+            self.bias = self._vector32(tensors[self.prefix + self.bias_leaf])
+
+    def forward(self, residual: torch.Tensor, delta, ctx, *, tag: str = "normed",
+                row_idx: Optional[torch.Tensor] = None, delta_scale: float = 1.0):
+        if isinstance(delta, FoldedNorm):        # made for another norm: the residual is already updated
+            delta = None
+        rows = residual.shape[0] if row_idx is None else row_idx.numel()
+        out = ctx.workspace.get(tag, (rows, self.size), ctx.dtype)
+        K.add_layer_norm(residual, delta, self.weight, self.bias, self.eps, out, row_idx, delta_scale)
+        return out
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "layer_norm", LayerNorm)

@@ -32,7 +32,7 @@ class RotaryEncoding(PositionEncoding):
         self.head_dim = int(self.p("head_dim"))
         self.rotary_dim = int(self.p("rotary_dim", self.head_dim))
         self.theta = float(self.p("theta"))
-        self.max_positions = int(self.p("max_positions"))
+        self.max_positions = int(self.p("max_positions", 0))     # 0: no table of positions (see `frequencies`)
         if self.rotary_dim % 2 or not (0 < self.rotary_dim <= self.head_dim):
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and within the head "
                              f"({self.head_dim})")
@@ -49,6 +49,19 @@ class RotaryEncoding(PositionEncoding):
             table = table.contiguous().to(self.rt.device)
             self.rt.shared[key] = table
         return table, self.rotary_dim
+
+
+    def frequencies(self) -> torch.Tensor:
+        """f_i = theta^(-2i/r), i in [0, r/2), as a 64-bit table on the device: for kernels that form the
+        angle position * f_i themselves (in double, so no table of positions and no longest position)."""
+        key = ("rotary_freq", self.rotary_dim, self.theta)
+        freq = self.rt.shared.get(key)
+        if freq is None:
+            i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+            freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.rotary_dim)
+            freq = freq.contiguous().to(self.rt.device)
+            self.rt.shared[key] = freq
+        return freq
 
 
 class NoPosition(PositionEncoding):
