@@ -278,9 +278,18 @@ def main() -> int:
     ap.add_argument("--no-decode", action="store_true", help="prefill measurement only (for profiling)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="model shape (default: the metric's 8b)")
+    ap.add_argument("--design", default=None, choices=["kolorax"],
+                    help="instead of the default workload: prefill and decode throughput of this design at a few sizes, "
+                         "beside Qwen3 dense at equal size, and its kernels against their floors")
+    ap.add_argument("--design-sizes", default="", help="with --design: the sizes to run, with commas (default: all)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        from firefly_b200.design_bench import main as design_main
+        if args.steps == 96:
+            args.steps = 32
+        return design_main(args, peaks())
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -51,6 +51,10 @@ class KoloraxConfig(ModelConfig):
     layers: Tuple[Mapping[str, Any], ...]
     loop: Optional[Mapping[str, int]] = None
 
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
     @classmethod
     def from_dict(cls, raw: Mapping[str, Any]) -> "KoloraxConfig":
         g = cls._get
@@ -98,8 +102,8 @@ class KoloraxConfig(ModelConfig):
                 rot = _need(mx, "rot", None, f"{where}.mixer")
                 _need(rot, "base", float, f"{where}.mixer.rot")
                 dims = int(rot.get("dims", mx["rot_dim"]))
-                if dims != int(mx["rot_dim"]) or dims % 2:
-                    raise ConfigError(f"config.json: {where}.mixer.rot.dims must equal rot_dim and be even "
+                if dims > int(mx["rot_dim"]) or dims % 2 or dims < 0:
+                    raise ConfigError(f"config.json: {where}.mixer.rot.dims must be even and at most rot_dim "
                                       f"(the rotated vector is the rot_dim part)")
             ml = L.get("mlp")
             if ml is not None:

@@ -1,6 +1,6 @@
 // Plain attention over the paged cache: one block per (query token, q head), scalar
 // 32-bit arithmetic throughout.  It serves the true 32-bit path and stands beside
-// the tensor-core kernel as its reference.  Any head size up to 256, any block
+// the tensor-core kernel as its reference.  Any head size up to 512, any block
 // size, any group size; prefill portions and decode tokens alike, since every
 // query is described only by its sequence and absolute position.
 //
@@ -19,7 +19,7 @@
 namespace ff {
 
 constexpr int ATT_WARPS = 4;
-constexpr int ATT_MAX_D = 256;
+constexpr int ATT_MAX_D = 512;
 constexpr int ATT_PER_LANE = ATT_MAX_D / 32;
 
 template <typename T>

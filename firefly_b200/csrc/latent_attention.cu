@@ -9,7 +9,8 @@
 // W_uv[h] out_latent[h].  This file finishes the query rows and writes the cache rows; the
 // attention itself is the paged attention the other mixers use.
 //
-// Rotation: pairs (i, i + rot_dim/2), angle = position * f_i.  The angle is formed in double from
+// Rotation: the first rdims (<= rot_dim) elements of the rotated part, pairs (i, i + rdims/2), angle =
+// position * f_i; elements past rdims pass unchanged.  The angle is formed in double from
 // the 64-bit frequency table and reduced there, so cos and sin are right to 32-bit rounding at
 // any position; norms and the rotation are 32-bit.
 #include "common.cuh"
@@ -23,12 +24,13 @@ __global__ void latent_finish_kernel(
     const float* __restrict__ c_norm_w, float eps, const double* __restrict__ freq /*[rot/2]*/,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ block_table,
     int max_blocks, int block_size, int num_blocks, T* __restrict__ cache /*[blocks, 2, 1, block, d]*/,
-    T* __restrict__ q_full /*[T, H, d]*/, int Ttot, int H, int dim, int rot, int kv_rank, int* __restrict__ status) {
+    T* __restrict__ q_full /*[T, H, d]*/, int Ttot, int H, int dim, int rot, int rdims, int kv_rank,
+    int* __restrict__ status) {
     pdl_prologue();
-    extern __shared__ float sh[];           // cos[rot/2], sin[rot/2]
+    extern __shared__ float sh[];           // cos[rdims/2], sin[rdims/2]
     __shared__ float scratch[32];
     const int t = blockIdx.x;
-    const int half = rot / 2;
+    const int half = rdims / 2, rest = rot - rdims;
     const int d = kv_rank + rot;
     const int pos = positions[t];
     float* s_cos = sh;
@@ -65,6 +67,10 @@ __global__ void latent_finish_kernel(
             vrow[kv_rank + i] = from_float<T>(0.f);
             vrow[kv_rank + half + i] = from_float<T>(0.f);
         }
+        for (int i = threadIdx.x; i < rest; i += blockDim.x) {
+            krow[kv_rank + rdims + i] = dkv[kv_rank + rdims + i];
+            vrow[kv_rank + rdims + i] = from_float<T>(0.f);
+        }
     }
     // the query rows: [q_abs | rotated part] per head
     T* qf = q_full + (size_t)t * H * d;
@@ -79,6 +85,10 @@ __global__ void latent_finish_kernel(
         const float a = to_float(qr[i]), b = to_float(qr[half + i]);
         qf[(size_t)h * d + kv_rank + i] = from_float<T>(a * s_cos[i] - b * s_sin[i]);
         qf[(size_t)h * d + kv_rank + half + i] = from_float<T>(b * s_cos[i] + a * s_sin[i]);
+    }
+    for (int idx = threadIdx.x; idx < H * rest; idx += blockDim.x) {
+        const int h = idx / rest, i = idx - h * rest;
+        qf[(size_t)h * d + kv_rank + rdims + i] = q[(size_t)h * (dim + rot) + dim + rdims + i];
     }
 }
 
@@ -104,20 +114,20 @@ using namespace ff;
 FF_EXPORT int ff_latent_finish(const void* proj, int dtype, int proj_stride, int q_off, int dkv_off, const void* q_abs,
                                const float* c_norm_w, float eps, const double* freq, const int* positions,
                                const int* token_seq, const int* block_table, int max_blocks, int block_size,
-                               int num_blocks, void* cache, void* q_full, int T, int H, int dim, int rot, int kv_rank,
-                               int* status, cudaStream_t stream) {
+                               int num_blocks, void* cache, void* q_full, int T, int H, int dim, int rot, int rdims,
+                               int kv_rank, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (rot < 0 || rot % 2 || kv_rank <= 0) return FF_ERR_BAD_ARG;
-    const size_t smem = (size_t)rot * sizeof(float);
+    if (rot < 0 || rdims < 0 || rdims > rot || rdims % 2 || kv_rank <= 0) return FF_ERR_BAD_ARG;
+    const size_t smem = (size_t)(rdims > 0 ? rdims : 2) * sizeof(float);
     if (smem > 40 * 1024) return FF_ERR_UNSUPPORTED;
     if (dtype == 0)
         FF_LAUNCH((latent_finish_kernel<float>), T, 256, smem, stream, (const float*)proj, proj_stride, q_off, dkv_off,
                   (const float*)q_abs, c_norm_w, eps, freq, positions, token_seq, block_table, max_blocks, block_size,
-                  num_blocks, (float*)cache, (float*)q_full, T, H, dim, rot, kv_rank, status);
+                  num_blocks, (float*)cache, (float*)q_full, T, H, dim, rot, rdims, kv_rank, status);
     else if (dtype == 1)
         FF_LAUNCH((latent_finish_kernel<bf16>), T, 256, smem, stream, (const bf16*)proj, proj_stride, q_off, dkv_off,
                   (const bf16*)q_abs, c_norm_w, eps, freq, positions, token_seq, block_table, max_blocks, block_size,
-                  num_blocks, (bf16*)cache, (bf16*)q_full, T, H, dim, rot, kv_rank, status);
+                  num_blocks, (bf16*)cache, (bf16*)q_full, T, H, dim, rot, rdims, kv_rank, status);
     else return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
     return 0;

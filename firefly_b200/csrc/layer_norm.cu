@@ -24,6 +24,18 @@ __global__ void add_layer_norm_kernel(float* __restrict__ residual, const TD* __
     float* res = residual + (size_t)src * H;
     const TD* dl = delta ? delta + (size_t)src * H : nullptr;
     float sum = 0.f;
+    if ((H & 3) == 0) {       // four elements a thread and step
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(res + i);
+            if (dl) {
+                v.x += delta_scale * to_float(dl[i]);     v.y += delta_scale * to_float(dl[i + 1]);
+                v.z += delta_scale * to_float(dl[i + 2]); v.w += delta_scale * to_float(dl[i + 3]);
+                if (write_residual) *reinterpret_cast<float4*>(res + i) = v;
+            }
+            *reinterpret_cast<float4*>(row + i) = v;
+            sum += (v.x + v.y) + (v.z + v.w);
+        }
+    } else
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = res[i];
         if (dl) {
@@ -77,7 +89,7 @@ FF_EXPORT int ff_add_layer_norm(float* residual, const void* delta, int delta_dt
     if (H <= 0) return FF_ERR_BAD_ARG;
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return FF_ERR_UNSUPPORTED;
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
 #define FF_LN(TD, TO)                                                                                        \
     do {                                                                                                     \
         if (smem > 48 * 1024) FF_SMEM_LIMIT((add_layer_norm_kernel<TD, TO>), smem);                          \

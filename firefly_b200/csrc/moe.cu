@@ -102,9 +102,9 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int T, int E, int 
 }
 
 // One block: rows sorted by expert.  seg[e] .. seg[e+1] are expert e's rows; row_of[entry] is
-// the row of (token, choice) = entry; src_tok[row] its token; the row tiles of MOE_BM rows
-// are listed as (expert, first row) with their count in n_tiles.
-__global__ void moe_plan_kernel(const int* __restrict__ ids, int entries, int top, int E, int* __restrict__ seg,
+// the row of (token, choice) = entry; src_tok[row] its token; the row tiles of row_tile rows
+// (64 for the plain grouped kernel, 128 for the tensor-core one) are listed as (expert, first row) with their count in n_tiles.
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int entries, int top, int E, int row_tile, int* __restrict__ seg,
                                 int* __restrict__ row_of, int* __restrict__ src_tok, int* __restrict__ tile_expert,
                                 int* __restrict__ tile_row0, int* __restrict__ n_tiles) {
     pdl_prologue();
@@ -121,7 +121,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int entries, int to
         for (int e = 0; e < E; ++e) {
             offs[e] = run;
             seg[e] = run;
-            for (int r0 = 0; r0 < counts[e]; r0 += MOE_BM) {
+            for (int r0 = 0; r0 < counts[e]; r0 += row_tile) {
                 tile_expert[nt] = e;
                 tile_row0[nt] = run + r0;
                 ++nt;
@@ -207,6 +207,141 @@ __global__ void __launch_bounds__(256) moe_grouped_kernel(
     }
 }
 
+// The same grouped product for bfloat16 on tensor cores: mma.sync m16n8k16 with 32-bit accumulation,
+// operands staged through a three-stage cp.async ring in shared memory (rows padded to 40 elements so
+// that the 32-bit fragment loads of a warp fall into 32 different banks).  A block takes 128 rows of one
+// expert (the plan is made with that row tile) and 128 rows of B: 64 columns of gate and the same 64 of up
+// when GATEUP, else 128 output columns.  Eight warps in a 2 x 4 grid, each 64 rows x 32 rows of B (16 gate +
+// 16 up columns, so that a thread holds both halves of an output).  Needs K % 8 == 0 (16-byte copies).  Rows
+// past the expert's last row and columns past N are filled with zeros by the copies and not stored.
+constexpr int MMA_BM = 128, MMA_BR = 128, MMA_BK = 32, MMA_LD = 40, MMA_STAGES = 3;
+constexpr size_t MMA_SMEM = (size_t)MMA_STAGES * (MMA_BM + MMA_BR) * MMA_LD * sizeof(bf16);
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+    const int bytes = pred ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GATEUP>
+__global__ void __launch_bounds__(256) moe_grouped_mma_kernel(
+    const bf16* __restrict__ a, const int* __restrict__ src_tok, const bf16* __restrict__ b0,
+    const bf16* __restrict__ b1, const int* __restrict__ seg, const int* __restrict__ tile_expert,
+    const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, void* __restrict__ out, int N, int K,
+    float limit) {
+    pdl_prologue();
+    if ((int)blockIdx.y >= n_tiles[0]) return;
+    extern __shared__ __align__(16) unsigned char mma_smem[];
+    typedef bf16 (*Tile)[MMA_BM][MMA_LD];                      // [stage][row][k]
+    Tile As = reinterpret_cast<Tile>(mma_smem);
+    Tile Bs = reinterpret_cast<Tile>(mma_smem + (size_t)MMA_STAGES * MMA_BM * MMA_LD * sizeof(bf16));
+    static_assert(MMA_BM == MMA_BR, "A and B tiles share a shape");
+    constexpr int COLS = GATEUP ? MMA_BR / 2 : MMA_BR;          // output columns of a block
+    const int e = tile_expert[blockIdx.y], row0 = tile_row0[blockIdx.y];
+    const int rows = min(MMA_BM, seg[e + 1] - row0);
+    const int n0 = blockIdx.x * COLS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 2, wn = warp & 3, g = lane >> 2, t4 = lane & 3;
+    // this thread's copies: rows tid / 4 and tid / 4 + 64 (of A and of B), 16-byte chunk tid % 4 of a stage's 32 columns.
+    // Row r of the B tile: GATEUP: warp wn's 32 rows are gate columns [16 wn, 16 wn + 16) then the same up columns;
+    // else output column r.
+    const int lr = tid >> 2, lc = (tid & 3) * 8;
+    const bf16* a_row[2];
+    const bf16* b_row[2];
+    bool a_ok[2], b_ok[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const int r = lr + 64 * q;
+        a_ok[q] = r < rows;
+        const int src = a_ok[q] ? (GATEUP ? src_tok[row0 + r] : row0 + r) : 0;
+        a_row[q] = a + (size_t)src * K;
+        int col;
+        const bf16* base = b0;
+        if (GATEUP) {
+            const int w = r >> 5, in = r & 31;
+            col = n0 + w * 16 + (in & 15);
+            if (in >= 16) base = b1;
+        } else {
+            col = n0 + r;
+        }
+        b_ok[q] = col < N;
+        b_row[q] = base + ((size_t)e * N + (b_ok[q] ? col : 0)) * K;
+    }
+    const int KT = (K + MMA_BK - 1) / MMA_BK;
+    auto load = [&](int stage, int kt) {
+        const int k = kt * MMA_BK + lc;
+        const bool in = k < K;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            cp_async16(&As[stage][lr + 64 * q][lc], a_row[q] + (in ? k : 0), in && a_ok[q]);
+            cp_async16(&Bs[stage][lr + 64 * q][lc], b_row[q] + (in ? k : 0), in && b_ok[q]);
+        }
+    };
+    float acc[4][4][4] = {};
+    for (int s = 0; s < MMA_STAGES - 1; ++s) {
+        if (s < KT) load(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kt = 0; kt < KT; ++kt) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(MMA_STAGES - 2) : "memory");
+        __syncthreads();
+        const int nxt = kt + MMA_STAGES - 1;
+        if (nxt < KT) load(nxt % MMA_STAGES, nxt);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int st = kt % MMA_STAGES;
+#pragma unroll
+        for (int kk = 0; kk < MMA_BK; kk += 16) {
+            uint32_t bfr[4][2];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int n = wn * 32 + nt * 8 + g;
+                bfr[nt][0] = *reinterpret_cast<const uint32_t*>(&Bs[st][n][kk + 2 * t4]);
+                bfr[nt][1] = *reinterpret_cast<const uint32_t*>(&Bs[st][n][kk + 8 + 2 * t4]);
+            }
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                const int r = wm * 64 + mt * 16 + g;
+                uint32_t af[4];
+                af[0] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 2 * t4]);
+                af[1] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 2 * t4]);
+                af[2] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 8 + 2 * t4]);
+                af[3] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 8 + 2 * t4]);
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) mma_bf16_16816(acc[mt][nt], af, bfr[nt][0], bfr[nt][1]);
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int r = wm * 64 + mt * 16 + g + (c >> 1) * 8;
+            if (r >= rows) continue;
+            if (GATEUP) {
+                // B rows 0..15 of the warp are gate (n tiles 0, 1), rows 16..31 the same columns of up (n tiles 2, 3)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int n = n0 + wn * 16 + nt * 8 + 2 * t4 + (c & 1);
+                    if (n < N)
+                        ((bf16*)out)[(size_t)(row0 + r) * N + n] =
+                            __float2bfloat16_rn(clamped_glu(acc[mt][nt][c], acc[mt][nt + 2][c], limit));
+                }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int n = n0 + wn * 32 + nt * 8 + 2 * t4 + (c & 1);
+                    if (n < N) ((float*)out)[(size_t)(row0 + r) * N + n] = acc[mt][nt][c];
+                }
+            }
+        }
+}
+
 // y[t, f] = clamped_glu(gu[t, f], gu[t, F + f])
 template <typename T>
 __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, int F, float limit, size_t total) {
@@ -237,7 +372,8 @@ __global__ void moe_combine_kernel(float* __restrict__ residual, const float* __
 
 using namespace ff;
 
-FF_EXPORT int ff_moe_row_tile() { return MOE_BM; }
+// rows of a row tile: of the tensor-core kernel (bfloat16, K % 8 == 0) or of the plain one
+FF_EXPORT int ff_moe_row_tile(int tensor_cores) { return tensor_cores ? MMA_BM : MOE_BM; }
 
 FF_EXPORT int ff_moe_route(const float* z, int T, int E, int top, int groups, int keep, int* ids, float* wts,
                            cudaStream_t stream) {
@@ -253,21 +389,40 @@ FF_EXPORT int ff_moe_route(const float* z, int T, int E, int top, int groups, in
     return 0;
 }
 
-FF_EXPORT int ff_moe_plan(const int* ids, int entries, int top, int E, int* seg, int* row_of, int* src_tok,
-                          int* tile_expert, int* tile_row0, int* n_tiles, cudaStream_t stream) {
+FF_EXPORT int ff_moe_plan(const int* ids, int entries, int top, int E, int row_tile, int* seg, int* row_of,
+                          int* src_tok, int* tile_expert, int* tile_row0, int* n_tiles, cudaStream_t stream) {
     if (entries <= 0) return 0;
+    if (row_tile != MOE_BM && row_tile != MMA_BM) return FF_ERR_BAD_ARG;
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
     if (smem > 48 * 1024) return FF_ERR_UNSUPPORTED;
-    FF_LAUNCH(moe_plan_kernel, 1, 1024, smem, stream, ids, entries, top, E, seg, row_of, src_tok, tile_expert, tile_row0,
-              n_tiles);
+    FF_LAUNCH(moe_plan_kernel, 1, 1024, smem, stream, ids, entries, top, E, row_tile, seg, row_of, src_tok, tile_expert,
+              tile_row0, n_tiles);
     FF_LAUNCH_CHECK();
     return 0;
 }
 
 FF_EXPORT int ff_moe_grouped(const void* a, const int* src_tok, const void* b0, const void* b1, int dtype, int gateup,
                              const int* seg, const int* tile_expert, const int* tile_row0, const int* n_tiles,
-                             void* out, int max_tiles, int N, int K, float limit, cudaStream_t stream) {
+                             void* out, int max_tiles, int N, int K, float limit, int tensor_cores,
+                             cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
+    if (tensor_cores) {
+        // the plan was made with 128-row tiles
+        if (dtype != 1 || K % 8 || ((((uintptr_t)a | (uintptr_t)b0 | (uintptr_t)b1) & 15) != 0)) return FF_ERR_BAD_ARG;
+        const int cols = gateup ? MMA_BR / 2 : MMA_BR;
+        dim3 grid((N + cols - 1) / cols, max_tiles);
+        if (gateup) {
+            FF_SMEM_LIMIT((moe_grouped_mma_kernel<true>), MMA_SMEM);
+            FF_LAUNCH((moe_grouped_mma_kernel<true>), grid, 256, MMA_SMEM, stream, (const bf16*)a, src_tok, (const bf16*)b0,
+                      (const bf16*)b1, seg, tile_expert, tile_row0, n_tiles, out, N, K, limit);
+        } else {
+            FF_SMEM_LIMIT((moe_grouped_mma_kernel<false>), MMA_SMEM);
+            FF_LAUNCH((moe_grouped_mma_kernel<false>), grid, 256, MMA_SMEM, stream, (const bf16*)a, src_tok, (const bf16*)b0,
+                      (const bf16*)b1, seg, tile_expert, tile_row0, n_tiles, out, N, K, limit);
+        }
+        FF_LAUNCH_CHECK();
+        return 0;
+    }
     dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
 #define FF_MOE(T, G)                                                                                               \
     FF_LAUNCH((moe_grouped_kernel<T, G>), grid, 256, 0, stream, (const T*)a, src_tok, (const T*)b0, (const T*)b1, seg, \

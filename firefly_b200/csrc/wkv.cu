@@ -9,7 +9,7 @@
 // The state (S and the last x of the sequence) lives in 32-bit in the request's state slot and
 // is carried from step to step; a fresh request starts from zeros.  Everything that enters the
 // recurrence is 32-bit: decays, the bonus u, S, the sums.  Tokens are walked one after the other,
-// so the result does not depend on how a prompt was cut into steps.
+// each with the same order of additions, so the result does not depend on how a prompt was cut into steps.
 #include "common.cuh"
 
 namespace ff {
@@ -49,74 +49,109 @@ __global__ void tanh_cast_kernel(const float* __restrict__ in, TO* __restrict__ 
 }
 
 constexpr int WKV_CHUNK = 8;     // tokens whose r, k, w are staged in shared memory at a time
+constexpr int WKV_PARTS = 4;     // threads that share a column of S: each holds a quarter of its key channels
 
-// One block per (sequence, head); thread j owns value channel j and column j of S in registers.
+// One block per (sequence, head).  A column j of S (value channel j) is held by WKV_PARTS neighbouring
+// threads, each with DIM / WKV_PARTS key channels in registers, so a token costs DIM / WKV_PARTS steps of the
+// serial chain and two shuffles.  The bonus term's factors p_i = r_i u_i k_i are formed while a chunk is
+// staged, so the inner loop has one multiply-add for it.
+//   o_j = sum_i (r_i S_ij + p_i v_j);   S_ij <- w_i S_ij + k_i v_j
 template <typename T, int DIM>
-__global__ void __launch_bounds__(DIM) wkv_scan_kernel(
+__global__ void __launch_bounds__(DIM * WKV_PARTS) wkv_scan_kernel(
     const T* __restrict__ rkvg /*[4,T,HD]*/, const float* __restrict__ dlog /*[T,HD]*/,
     const float* __restrict__ w0, const float* __restrict__ u, float* __restrict__ state, size_t state_stride,
     int prev_off, const T* __restrict__ x, int W, const int* __restrict__ cu_q,
     const int* __restrict__ state_slots, const int* __restrict__ seq_fresh, float* __restrict__ o /*[T,HD]*/,
     int Ttot, int heads, int dim) {
     pdl_prologue();
-    __shared__ float s_r[WKV_CHUNK][DIM], s_k[WKV_CHUNK][DIM], s_w[WKV_CHUNK][DIM], s_u[DIM];
-    const int s = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+    constexpr int KP = DIM / WKV_PARTS;          // key channels a thread holds
+    __shared__ __align__(16) float s_r[WKV_CHUNK][DIM], s_k[WKV_CHUNK][DIM], s_w[WKV_CHUNK][DIM], s_p[WKV_CHUNK][DIM];
+    __shared__ float s_v[WKV_CHUNK][DIM];
+    const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    // thread `part` of a column holds key channels 16 m + 4 part + e (m < KP / 4, e < 4): the four parts of a
+    // column then read four neighbouring 16-byte pieces of shared memory, which lie in different banks
+    const int j = tid / WKV_PARTS, part = tid % WKV_PARTS;
+    auto chan = [&](int i) { return (i >> 2) * (4 * WKV_PARTS) + part * 4 + (i & 3); };
     const int t0 = cu_q[s], t1 = cu_q[s + 1];
     const int HD = heads * dim;
     const bool live = j < dim;
     float* st = state + (size_t)state_slots[s] * state_stride;
-    float* S_g = st + (size_t)h * dim * dim;
+    // A head's state is kept in the slot as this kernel's threads hold it: element (register i, thread tid) at
+    // i * blockDim + tid, DIM * DIM floats a head, so that loading and storing it is coalesced.  Only this kernel
+    // reads it, and a layer always runs the same instantiation.
+    float* S_g = st + (size_t)h * DIM * DIM;
     const bool fresh = seq_fresh[s] != 0;
-    float S[DIM];
+    float S[KP];
 #pragma unroll
-    for (int i = 0; i < DIM; ++i) S[i] = (live && i < dim && !fresh) ? S_g[(size_t)i * dim + j] : 0.f;
-    s_u[j] = live ? u[h * dim + j] : 0.f;
-    const float w0j = live ? w0[h * dim + j] : 0.f;
+    for (int i = 0; i < KP; ++i) S[i] = (live && chan(i) < dim && !fresh) ? S_g[i * (DIM * WKV_PARTS) + tid] : 0.f;
+    // staging: thread c < dim takes channel c of every token of a chunk.  The next chunk's values are asked
+    // for (into registers) before the current chunk is computed, so their latency hides behind the recurrence.
+    const bool stager = tid < DIM, s_live = tid < dim;
+    const float w0c = (stager && s_live) ? w0[h * dim + tid] : 0.f;
+    const float uc = (stager && s_live) ? u[h * dim + tid] : 0.f;
     const T* r_in = rkvg;
     const T* k_in = rkvg + (size_t)Ttot * HD;
     const T* v_in = rkvg + (size_t)2 * Ttot * HD;
-    for (int c0 = t0; c0 < t1; c0 += WKV_CHUNK) {
-        const int n = min(WKV_CHUNK, t1 - c0);
-        float v[WKV_CHUNK];
-        __syncthreads();
+    T rn[WKV_CHUNK], kn[WKV_CHUNK], vn[WKV_CHUNK];
+    float dn[WKV_CHUNK];
+    auto fetch = [&](int c0) {
 #pragma unroll
         for (int c = 0; c < WKV_CHUNK; ++c) {
-            if (c < n && live) {
-                const size_t at = (size_t)(c0 + c) * HD + h * dim + j;
-                s_r[c][j] = to_float(r_in[at]);
-                s_k[c][j] = to_float(k_in[at]);
-                s_w[c][j] = expf(-expf(dlog[at] + w0j));
-                v[c] = to_float(v_in[at]);
-            } else {
-                s_r[c][j] = 0.f; s_k[c][j] = 0.f; s_w[c][j] = 1.f;
-                v[c] = 0.f;
+            const bool in = stager && s_live && c0 + c < t1;
+            const size_t at = in ? (size_t)(c0 + c) * HD + h * dim + tid : 0;
+            rn[c] = in ? r_in[at] : from_float<T>(0.f);
+            kn[c] = in ? k_in[at] : from_float<T>(0.f);
+            vn[c] = in ? v_in[at] : from_float<T>(0.f);
+            dn[c] = in ? dlog[at] : 0.f;
+        }
+    };
+    fetch(t0);
+    for (int c0 = t0; c0 < t1; c0 += WKV_CHUNK) {
+        const int n = min(WKV_CHUNK, t1 - c0);
+        __syncthreads();
+        if (stager) {
+#pragma unroll
+            for (int c = 0; c < WKV_CHUNK; ++c) {
+                const bool in = s_live && c < n;
+                const float rv = to_float(rn[c]), kv = to_float(kn[c]);
+                s_r[c][tid] = rv;
+                s_k[c][tid] = kv;
+                s_v[c][tid] = to_float(vn[c]);
+                s_w[c][tid] = in ? expf(-expf(dn[c] + w0c)) : 1.f;
+                s_p[c][tid] = rv * uc * kv;
             }
         }
         __syncthreads();
+        if (c0 + WKV_CHUNK < t1) fetch(c0 + WKV_CHUNK);
 #pragma unroll
         for (int c = 0; c < WKV_CHUNK; ++c) {
             if (c < n) {
-                const float vj = v[c];
+                const float vj = s_v[c][j];
                 float acc = 0.f;
 #pragma unroll
-                for (int i = 0; i < DIM; ++i) {
-                    const float kv = s_k[c][i] * vj;
-                    acc += s_r[c][i] * (S[i] + s_u[i] * kv);
-                    S[i] = s_w[c][i] * S[i] + kv;
+                for (int i = 0; i < KP; i += 4) {
+                    const int at = i * WKV_PARTS + part * 4;      // = chan(i), i a multiple of 4
+                    const float4 r4 = *reinterpret_cast<const float4*>(&s_r[c][at]);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&s_k[c][at]);
+                    const float4 w4 = *reinterpret_cast<const float4*>(&s_w[c][at]);
+                    const float4 p4 = *reinterpret_cast<const float4*>(&s_p[c][at]);
+                    acc += r4.x * S[i] + p4.x * vj;     S[i]     = w4.x * S[i]     + k4.x * vj;
+                    acc += r4.y * S[i + 1] + p4.y * vj; S[i + 1] = w4.y * S[i + 1] + k4.y * vj;
+                    acc += r4.z * S[i + 2] + p4.z * vj; S[i + 2] = w4.z * S[i + 2] + k4.z * vj;
+                    acc += r4.w * S[i + 3] + p4.w * vj; S[i + 3] = w4.w * S[i + 3] + k4.w * vj;
                 }
-                if (live) o[(size_t)(c0 + c) * HD + h * dim + j] = acc;
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                if (live && part == 0) o[(size_t)(c0 + c) * HD + h * dim + j] = acc;
             }
         }
     }
-    if (live) {
 #pragma unroll
-        for (int i = 0; i < DIM; ++i)
-            if (i < dim) S_g[(size_t)i * dim + j] = S[i];
-    }
+    for (int i = 0; i < KP; ++i) S_g[i * (DIM * WKV_PARTS) + tid] = (live && chan(i) < dim) ? S[i] : 0.f;
     // the sequence's last input row, for the first token of its next step
     if (h == 0 && t1 > t0) {
         const T* last = x + (size_t)(t1 - 1) * W;
-        for (int i = j; i < W; i += DIM) st[prev_off + i] = to_float(last[i]);
+        for (int i = tid; i < W; i += DIM * WKV_PARTS) st[prev_off + i] = to_float(last[i]);
     }
 }
 
@@ -176,7 +211,7 @@ static int wkv_scan_launch(const void* rkvg, const float* dlog, const float* w0,
                            int dim, cudaStream_t stream) {
     dim3 grid(n_seqs, heads);
 #define FF_WKV(D)                                                                                                  \
-    FF_LAUNCH((wkv_scan_kernel<T, D>), grid, D, 0, stream, (const T*)rkvg, dlog, w0, u, state, (size_t)state_stride, \
+    FF_LAUNCH((wkv_scan_kernel<T, D>), grid, D * WKV_PARTS, 0, stream, (const T*)rkvg, dlog, w0, u, state, (size_t)state_stride, \
               prev_off, (const T*)x, W, cu_q, state_slots, seq_fresh, o, Ttot, heads, dim)
     if (dim <= 32) FF_WKV(32);
     else if (dim <= 64) FF_WKV(64);
@@ -186,6 +221,9 @@ static int wkv_scan_launch(const void* rkvg, const float* dlog, const float* w0,
     FF_LAUNCH_CHECK();
     return 0;
 }
+
+// the head size the recurrence kernel is instantiated for (its state keeps that many squared floats a head)
+FF_EXPORT int ff_wkv_state_dim(int dim) { return dim <= 32 ? 32 : (dim <= 64 ? 64 : (dim <= 128 ? 128 : -1)); }
 
 FF_EXPORT int ff_wkv_scan(const void* rkvg, int dtype, const float* dlog, const float* w0, const float* u, float* state,
                           long long state_stride, int prev_off, const void* x, int W, const int* cu_q,

@@ -38,7 +38,8 @@ def kolorax_spec(cfg: KoloraxConfig) -> ModelSpec:
                 hidden_size=W, heads=int(mx["heads"]), dim=int(mx["dim"]), rot_dim=int(mx["rot_dim"]),
                 vdim=int(mx["vdim"]), kv_rank=int(mx["kv_rank"]), scale=float(mx["scale"]), eps=cfg.norm_eps),
                 prefix=f"{p}.mix")
-            position = PartSpec("rotary", dict(head_dim=int(mx["rot_dim"]), rotary_dim=int(mx["rot_dim"]),
+            position = PartSpec("rotary", dict(head_dim=int(mx["rot_dim"]),
+                                               rotary_dim=int(mx["rot"].get("dims", mx["rot_dim"])),
                                                theta=float(mx["rot"]["base"]), max_positions=0))
         ml = L.get("mlp")
         ff = None

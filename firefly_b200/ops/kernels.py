@@ -803,18 +803,27 @@ def tanh_cast(src: torch.Tensor, out: torch.Tensor) -> None:
 WKV_MAX_DIM = 128
 
 
+def wkv_state_dim(dim: int) -> int:
+    """The head size the recurrence kernel keeps its state for (the next of 32, 64, 128): a head's state takes
+    that many squared floats in the request's slot, in the kernel's own order."""
+    if not (0 < dim <= WKV_MAX_DIM):
+        raise KernelError(f"wkv: head size {dim} is not supported (1..{WKV_MAX_DIM})")
+    return 32 if dim <= 32 else (64 if dim <= 64 else 128)
+
+
 def wkv_scan(rkvg, dlog, w0, u, state, prev_off: int, x, ctx, o, heads: int, dim: int) -> None:
     """The recurrence, token by token, one block per (sequence, head).  rkvg [4,T,heads*dim] (r, k, v, gate
     projections; the gate is not read here), dlog float32 [T,heads*dim] (the decay's inner logarithm without
-    its offset w0), state float32 [slots, heads*dim*dim + W] (read unless the request is fresh, written back,
-    and the portion's last row of x saved behind it), o float32 [T, heads*dim]."""
+    its offset w0), state float32 [slots, prev_off + W] with prev_off >= heads * wkv_state_dim(dim)^2 (read unless
+    the request is fresh, written back in the kernel's own order, the portion's last row of x saved at prev_off),
+    o float32 [T, heads*dim]."""
     _need_cuda(rkvg, dlog, w0, u, state, x, o)
     T, W = x.shape
     HD = heads * dim
     assert rkvg.shape == (4, T, HD) and rkvg.dtype == x.dtype and dlog.shape == (T, HD) and dlog.dtype == torch.float32
     assert o.shape == (T, HD) and o.dtype == torch.float32 and state.dtype == torch.float32
     assert w0.dtype == u.dtype == torch.float32 and w0.numel() == HD and u.numel() == HD
-    assert state.shape[1] >= prev_off + W and prev_off >= heads * dim * dim
+    assert state.shape[1] >= prev_off + W and prev_off >= heads * wkv_state_dim(dim) ** 2
     _check(_lib("wkv").ff_wkv_scan(_p(rkvg), c_int(_dt(rkvg)), _p(dlog), _p(w0), _p(u), _p(state),
                                   ctypes.c_longlong(state.stride(0)), c_int(prev_off), _p(x), c_int(W), _p(ctx.cu_q),
                                   _p(ctx.state_slots), _p(ctx.seq_fresh), _p(o), c_int(T), c_int(ctx.num_seqs),
@@ -834,22 +843,24 @@ def wkv_out(o, gate, norm_w, eps: float, y, heads: int, dim: int) -> None:
 # --------------------------------------------------------------------------- #
 # attention over a cached latent vector (csrc/latent_attention.cu)
 def latent_finish(proj, q_off: int, dkv_off: int, q_abs, c_norm_w, eps: float, freq, ctx, table, pages, q_full,
-                  heads: int, dim: int, rot: int, kv_rank: int) -> None:
+                  heads: int, dim: int, rot: int, kv_rank: int, rotary_dims: Optional[int] = None) -> None:
     """Finish a step's query rows and write its cache rows.  proj [T, *] holds the q heads ([heads, dim + rot]
     from column q_off) and the down projection ([kv_rank + rot] from column dkv_off); q_abs [heads, T, kv_rank];
-    freq float64 [rot/2]; pages [blocks, 2, 1, block, kv_rank + rot]; q_full [T, heads * (kv_rank + rot)]."""
+    freq float64 [rotary_dims/2] (rotary_dims <= rot, by default rot: the first that many elements of the rotated
+    part turn, the rest pass); pages [blocks, 2, 1, block, kv_rank + rot]; q_full [T, heads * (kv_rank + rot)]."""
+    rdims = rot if rotary_dims is None else int(rotary_dims)
     _need_cuda(proj, q_abs, c_norm_w, freq, table, pages, q_full)
     T = proj.shape[0]
     d = kv_rank + rot
     num_blocks, two, one, block_size, cd = pages.shape
     assert two == 2 and one == 1 and cd == d and pages.dtype == proj.dtype == q_abs.dtype == q_full.dtype
     assert q_abs.shape == (heads, T, kv_rank) and q_full.shape == (T, heads * d)
-    assert freq.dtype == torch.float64 and freq.numel() == rot // 2 and c_norm_w.dtype == torch.float32
+    assert freq.dtype == torch.float64 and freq.numel() == rdims // 2 and c_norm_w.dtype == torch.float32
     _check(_lib("latent_attention").ff_latent_finish(
         _p(proj), c_int(_dt(proj)), c_int(proj.stride(0)), c_int(q_off), c_int(dkv_off), _p(q_abs), _p(c_norm_w),
         c_float(eps), _p(freq), _p(ctx.positions), _p(ctx.token_seq), _p(table), c_int(table.shape[1]),
         c_int(block_size), c_int(num_blocks), _p(pages), _p(q_full), c_int(T), c_int(heads), c_int(dim), c_int(rot),
-        c_int(kv_rank), _p(ctx.status), _stream()), "latent_finish")
+        c_int(rdims), c_int(kv_rank), _p(ctx.status), _stream()), "latent_finish")
 
 
 def latent_gate(val, g, y, heads: int, vdim: int) -> None:
@@ -865,9 +876,18 @@ def latent_gate(val, g, y, heads: int, vdim: int) -> None:
 
 # --------------------------------------------------------------------------- #
 # routed experts (csrc/moe.cu)
+MOE_FORCE_PLAIN = False     # tests flip this to hold the tensor-core grouped product against the plain one
+
+
+def moe_on_tensor_cores(dtype: torch.dtype, k_sizes) -> bool:
+    """True if a layer's grouped products run on the tensor-core kernel: bfloat16 and every K a multiple of 8."""
+    return not MOE_FORCE_PLAIN and dtype == torch.bfloat16 and all(int(k) % 8 == 0 for k in k_sizes)
+
+
 @functools.lru_cache(maxsize=None)
-def moe_row_tile() -> int:
-    return int(_lib("moe").ff_moe_row_tile())
+def moe_row_tile(tensor_cores: bool) -> int:
+    """Rows of a row tile of the grouped product (the plan is made for the kernel that will run)."""
+    return int(_lib("moe").ff_moe_row_tile(c_int(1 if tensor_cores else 0)))
 
 
 def moe_route(z, ids, wts, groups: int, keep: int) -> None:
@@ -880,34 +900,39 @@ def moe_route(z, ids, wts, groups: int, keep: int) -> None:
                                    _stream()), "moe_route")
 
 
-def moe_plan(ids, E: int, seg, row_of, src_tok, tile_expert, tile_row0, n_tiles) -> None:
-    """Sort the step's (token, choice) pairs by expert, on the device (all int32)."""
+def moe_max_tiles(entries: int, E: int, tensor_cores: bool = False) -> int:
+    """The most row tiles `entries` rows spread over E experts can make."""
+    return entries // moe_row_tile(bool(tensor_cores)) + min(E, entries)
+
+
+def moe_plan(ids, E: int, seg, row_of, src_tok, tile_expert, tile_row0, n_tiles, tensor_cores: bool = False) -> None:
+    """Sort the step's (token, choice) pairs by expert, on the device (all int32), and list the row tiles for
+    the grouped kernel that will run (``tensor_cores``)."""
     _need_cuda(ids, seg, row_of, src_tok, tile_expert, tile_row0, n_tiles)
     T, top = ids.shape
+    cap = moe_max_tiles(T * top, E, tensor_cores)
     assert seg.numel() >= E + 1 and row_of.numel() >= T * top and src_tok.numel() >= T * top
-    assert tile_expert.numel() >= moe_max_tiles(T * top, E) and tile_row0.numel() >= moe_max_tiles(T * top, E)
-    _check(_lib("moe").ff_moe_plan(_p(ids), c_int(T * top), c_int(top), c_int(E), _p(seg), _p(row_of), _p(src_tok),
-                                  _p(tile_expert), _p(tile_row0), _p(n_tiles), _stream()), "moe_plan")
+    assert tile_expert.numel() >= cap and tile_row0.numel() >= cap
+    _check(_lib("moe").ff_moe_plan(_p(ids), c_int(T * top), c_int(top), c_int(E), c_int(moe_row_tile(bool(tensor_cores))),
+                                  _p(seg), _p(row_of), _p(src_tok), _p(tile_expert), _p(tile_row0), _p(n_tiles),
+                                  _stream()), "moe_plan")
 
 
-def moe_max_tiles(entries: int, E: int) -> int:
-    """The most row tiles `entries` rows spread over E experts can make."""
-    return entries // moe_row_tile() + min(E, entries)
-
-
-def moe_grouped(a, src_tok, b0, b1, plan, out, limit: float = 0.0) -> None:
+def moe_grouped(a, src_tok, b0, b1, plan, out, limit: float = 0.0, tensor_cores: bool = False) -> None:
     """Grouped product over the experts' stacked matrices.  With ``b1`` (gate|up): rows of ``a`` [T,K] gathered
     by src_tok, b0/b1 [E,N,K], out[row] = g * sigmoid(1.702 g) * (u + 1) with the clamps of ``limit``, in a's
     type.  Without: a [rows,K] in place, out float32 [rows,N].  ``plan`` = (seg, tile_expert, tile_row0, n_tiles,
-    max_tiles)."""
+    max_tiles), made with the same ``tensor_cores``: the mma.sync kernel (bfloat16, K % 8 == 0) or the plain one."""
     seg, tile_expert, tile_row0, n_tiles, max_tiles = plan
     _need_cuda(a, src_tok, b0, b1, out)
     E, N, Kd = b0.shape
     assert a.shape[1] == Kd and a.dtype == b0.dtype and out.shape[1] == N
     assert out.dtype == (a.dtype if b1 is not None else torch.float32)
+    assert not tensor_cores or (a.dtype == torch.bfloat16 and Kd % 8 == 0)
     _check(_lib("moe").ff_moe_grouped(_p(a), _p(src_tok), _p(b0), _p(b1), c_int(_dt(a)), c_int(1 if b1 is not None else 0),
                                      _p(seg), _p(tile_expert), _p(tile_row0), _p(n_tiles), _p(out), c_int(max_tiles),
-                                     c_int(N), c_int(Kd), c_float(limit), _stream()), "moe_grouped")
+                                     c_int(N), c_int(Kd), c_float(limit), c_int(1 if tensor_cores else 0),
+                                     _stream()), "moe_grouped")
 
 
 def clamped_glu(gu, y, limit: float) -> None:

@@ -14,7 +14,8 @@ values are their first kv_rank elements: the paged attention kernels of the othe
 rotate-half over the rot_dim part, angle = position * base^(-2i/rot_dim), formed in double.
 
 Parameters: hidden_size, heads, dim, rot_dim, vdim, kv_rank, scale, eps (of the latent's norm),
-cache_block_size (optional).  Position part: ``rotary`` with head_dim = rotary_dim = rot_dim.
+cache_block_size (optional).  Position part: ``rotary`` with head_dim = rot_dim and rotary_dim <= rot_dim
+(the first rotary_dim elements of the rotated part turn, the rest pass unchanged).
 Tensors: q [heads*(dim+rot_dim), W]; dkv [kv_rank+rot_dim, W]; dkv.norm [kv_rank];
 uk [heads*dim, kv_rank]; uv [heads*vdim, kv_rank]; g [heads*vdim, W]; o [W, heads*vdim].
 """
@@ -49,12 +50,14 @@ class LatentAttention(Part):
         self.cache_block_size = self.p("cache_block_size", None)
         self.position = position
         self.d = self.rank + self.rot                      # size of a cache row and of a finished query head
-        if self.rot % 2:
-            raise ValueError(f"{self.prefix}: rot_dim {self.rot} must be even")
         if self.rot and (position is None or not hasattr(position, "frequencies")):
             raise ValueError(f"{self.prefix}: needs a rotary position part")
-        if self.d > 256:
-            raise ValueError(f"{self.prefix}: kv_rank + rot_dim = {self.d} > 256 is not supported by the attention kernels")
+        # the first rotary_dim elements of the rot_dim part turn (all of them unless the position part says fewer)
+        self.rdims = int(getattr(position, "rotary_dim", 0)) if self.rot else 0
+        if self.rdims % 2 or self.rdims > self.rot:
+            raise ValueError(f"{self.prefix}: {self.rdims} rotated dimensions do not fit rot_dim {self.rot}")
+        if self.d > 512:
+            raise ValueError(f"{self.prefix}: kv_rank + rot_dim = {self.d} > 512 is not supported by the attention kernels")
         self.n_q, self.n_dkv, self.n_g = self.heads * (self.dim + self.rot), self.d, self.heads * self.vdim
         self.w_in = self.w_uk = self.w_uv = self.w_o = self.c_norm = None
 
@@ -106,9 +109,9 @@ class LatentAttention(Part):
         K.batched_linear(q_plain, self.w_uk, q_abs)
         pages, table = ctx.kv(slot)
         q_full = ws.get("lat.q_full", (T, H * d), dt)
-        freq = self.position.frequencies() if self.rot else torch.empty(0, dtype=torch.float64, device=x.device)
+        freq = self.position.frequencies() if self.rdims else torch.empty(0, dtype=torch.float64, device=x.device)
         K.latent_finish(proj, 0, self.n_q, q_abs, self.c_norm, self.eps, freq, ctx, table, pages, q_full,
-                        H, self.dim, self.rot, self.rank)
+                        H, self.dim, self.rot, self.rank, self.rdims)
         att = ws.get("lat.att", (T, H * d), dt)
         K.paged_attention(q_full, H * d, pages, table, ctx, att, H, 1, d, self.scale, 0)
         latent = att.view(T, H, d)[:, :, :self.rank].transpose(0, 1)

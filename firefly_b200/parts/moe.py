@@ -9,7 +9,7 @@
 
 All of it stays on the device (``csrc/moe.cu``): the router's choice, a plan that sorts the step's
 (token, choice) pairs by expert, two grouped products over the experts' stacked matrices (the first with
-the activation in its epilogue) and one kernel that forms the weighted sum, adds the shared expert and
+the activation in its epilogue; bfloat16 on tensor cores) and one kernel that forms the weighted sum, adds the shared expert and
 adds the whole, times the block's multiplier, into the 32-bit residual.  No count is read by the host,
 so steps with routed experts are captured into CUDA graphs like any other.
 
@@ -103,19 +103,20 @@ class GroupedExperts(Part):
         wts = ws.get("moe.wts", (T, top), torch.float32)
         K.moe_route(z, ids, wts, self.groups, self.keep)
         rows = T * top
-        max_tiles = K.moe_max_tiles(rows, self.E)
+        tc = K.moe_on_tensor_cores(dt, (W, self.ff))       # which grouped kernel runs: the plan's row tile is its
+        max_tiles = K.moe_max_tiles(rows, self.E, tc)
         seg = ws.get("moe.seg", (self.E + 1,), torch.int32)
         row_of = ws.get("moe.row_of", (rows,), torch.int32)
         src_tok = ws.get("moe.src_tok", (rows,), torch.int32)
         tile_e = ws.get("moe.tile_e", (max_tiles,), torch.int32)
         tile_r = ws.get("moe.tile_r", (max_tiles,), torch.int32)
         n_tiles = ws.get("moe.n_tiles", (1,), torch.int32)
-        K.moe_plan(ids, self.E, seg, row_of, src_tok, tile_e, tile_r, n_tiles)
+        K.moe_plan(ids, self.E, seg, row_of, src_tok, tile_e, tile_r, n_tiles, tc)
         plan = (seg, tile_e, tile_r, n_tiles, max_tiles)
         act = ws.get("moe.act", (rows, self.ff), dt)
-        K.moe_grouped(x, src_tok, self.w_gate, self.w_up, plan, act, self.limit)
+        K.moe_grouped(x, src_tok, self.w_gate, self.w_up, plan, act, self.limit, tc)
         outs = ws.get("moe.rows", (rows, W), torch.float32)
-        K.moe_grouped(act, src_tok, self.w_down, None, plan, outs)
+        K.moe_grouped(act, src_tok, self.w_down, None, plan, outs, 0.0, tc)
         shared = None
         if self.shared_ff:
             gu = ws.get("moe.sh_gu", (T, 2 * self.shared_ff), dt)

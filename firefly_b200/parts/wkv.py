@@ -47,7 +47,8 @@ class WKVMixer(Part):
         self.hd = self.heads * self.dim
         if self.dim > K.WKV_MAX_DIM:
             raise ValueError(f"{self.prefix}: head size {self.dim} > {K.WKV_MAX_DIM} is not supported by the recurrence kernel")
-        self.prev_off = self.heads * self.dim * self.dim        # where the last input row lies in the state
+        # the slot: every head's state as the recurrence kernel keeps it, then the last input row
+        self.prev_off = self.heads * K.wkv_state_dim(self.dim) ** 2
         self.w_rkvg = self.w1 = self.w2 = self.w_o = self.mu = self.w0 = self.u = self.norm = None
 
     def cache_spec(self):

@@ -27,8 +27,11 @@ def rms_unit(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
-def rotate_half(x, positions, base):
-    """x [T, r]; pairs (i, i + r/2); angle = position * base^(-2i/r)."""
+def rotate_half(x, positions, base, dims=None):
+    """x [T, n]; the first r = dims (default n) elements turn, pairs (i, i + r/2), angle = position * base^(-2i/r);
+    the rest pass unchanged."""
+    if dims is not None and dims < x.shape[-1]:
+        return torch.cat([rotate_half(x[..., :dims], positions, base), x[..., dims:]], dim=-1)
     r = x.shape[-1]
     half = r // 2
     f = torch.tensor([base ** (-2.0 * i / r) for i in range(half)], dtype=x.dtype)
@@ -67,16 +70,17 @@ def wkv_mixer(h, w, p, heads, dim, eps, state=None):
 
 
 # ------------------------------------------------------- latent attention mixer --
-def latent_attention_mixer(h, w, p, positions, *, heads, dim, rot_dim, vdim, kv_rank, scale, base, eps, cached=None):
+def latent_attention_mixer(h, w, p, positions, *, heads, dim, rot_dim, vdim, kv_rank, scale, base, eps, cached=None,
+                           rot_dims=None):
     """h [T, W] at ``positions``.  cached: None or (c [n, kv_rank], k_rot [n, rot_dim]) of earlier tokens.
     Returns (out [T, W], (c, k_rot) of all tokens so far)."""
     T = h.shape[0]
     q = (h @ w[f"{p}.q"].T).view(T, heads, dim + rot_dim)
     q_plain, q_rot = q[..., :dim], q[..., dim:]
-    q_rot = torch.stack([rotate_half(q_rot[:, hh], positions, base) for hh in range(heads)], dim=1)
+    q_rot = torch.stack([rotate_half(q_rot[:, hh], positions, base, rot_dims) for hh in range(heads)], dim=1)
     dkv = h @ w[f"{p}.dkv"].T
     c = rms_unit(dkv[:, :kv_rank], eps) * w[f"{p}.dkv.norm"]
-    k_rot = rotate_half(dkv[:, kv_rank:], positions, base)
+    k_rot = rotate_half(dkv[:, kv_rank:], positions, base, rot_dims)
     if cached is not None:
         c = torch.cat([cached[0], c])
         k_rot = torch.cat([cached[1], k_rot])
@@ -166,7 +170,7 @@ def forward(cfg, w, tokens, *, return_layers=False):
         elif L["type"] == "latent_attention":
             a, _ = latent_attention_mixer(hn, w, f"{p}.mix", pos, heads=mx["heads"], dim=mx["dim"], rot_dim=mx["rot_dim"],
                                           vdim=mx["vdim"], kv_rank=mx["kv_rank"], scale=mx["scale"],
-                                          base=mx["rot"]["base"], eps=eps)
+                                          base=mx["rot"]["base"], eps=eps, rot_dims=mx["rot"].get("dims"))
         else:
             raise ValueError(L["type"])
         x = x + m * a

@@ -606,9 +606,9 @@ def test_kernels_refuse_cpu_tensors_and_bad_sizes():
     k = K()
     with pytest.raises(k.KernelError, match="CUDA device only"):
         k.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
-    q = torch.zeros(1, 300, device="cuda")
-    pages = torch.zeros(2, 2, 1, 16, 300, device="cuda")
+    q = torch.zeros(1, 600, device="cuda")
+    pages = torch.zeros(2, 2, 1, 16, 600, device="cuda")
     z = torch.zeros(1, dtype=torch.int32, device="cuda")
     with pytest.raises(k.KernelError, match="not supported"):
-        k.paged_attention_simt(q, 300, pages, torch.zeros(1, 2, dtype=torch.int32, device="cuda"), z, z,
-                               torch.zeros(1, 300, device="cuda"), 1, 1, 300, 1.0, 0, z)
+        k.paged_attention_simt(q, 600, pages, torch.zeros(1, 2, dtype=torch.int32, device="cuda"), z, z,
+                               torch.zeros(1, 600, device="cuda"), 1, 1, 600, 1.0, 0, z)
