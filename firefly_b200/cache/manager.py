@@ -45,11 +45,11 @@ class KVGroup:
     block_size: int                       # tokens per page of this group
     num_blocks: int                       # usable pages of this group (the scratch page comes on top)
     allocator: BlockAllocator
-    storage: Optional[torch.Tensor] = None  # [n_slots, 1+num_blocks, 2, nkv, block, d]
+    storage: Optional[torch.Tensor] = None  # [n_slots, 1+num_blocks, planes, nkv, block, d]
 
     def bytes_per_token(self, dtype: torch.dtype) -> int:
         es = torch.empty((), dtype=dtype).element_size()
-        return len(self.slots) * 2 * self.spec.num_kv_heads * self.spec.head_dim * es
+        return len(self.slots) * self.spec.planes * self.spec.num_kv_heads * self.spec.head_dim * es
 
     def pages_for(self, ctx: int, new_tokens: int) -> int:
         """Pages a request must hold in this group to run ``new_tokens`` tokens behind ``ctx`` cached
@@ -139,14 +139,14 @@ class CacheManager:
 
     def allocate_storage(self, dtype: torch.dtype, device) -> None:
         for g in self.groups:
-            g.storage = torch.zeros((len(g.slots), 1 + g.num_blocks, 2, g.spec.num_kv_heads,
+            g.storage = torch.zeros((len(g.slots), 1 + g.num_blocks, g.spec.planes, g.spec.num_kv_heads,
                                      g.block_size, g.spec.head_dim), dtype=dtype, device=device)
         for slot, spec in self.state_specs.items():
             self.state_storage[slot] = torch.zeros((1 + self.max_requests, *spec.shape),
                                                    dtype=spec.dtype, device=device)
 
     def kv_view(self, slot: int) -> Tuple[torch.Tensor, int]:
-        """(pages of this slot [1+num_blocks, 2, nkv, block, d], group index)."""
+        """(pages of this slot [1+num_blocks, planes, nkv, block, d], group index)."""
         g = self.slot_group[slot]
         return self.groups[g].slot_view(slot), g
 

@@ -13,13 +13,15 @@ class PagedKVSpec:
     of a sequence are ever read, so pages that a window has passed are given
     back.  None: all keys are kept while the request lives.  ``block_size``:
     tokens per page if the mixer wants a page size of its own (None: the
-    engine's).  Slots with equal specs share a group: one pool, one table per
-    request."""
+    engine's).  ``planes``: 2 = a plane of keys and a plane of values per page; 1 = one
+    vector per token that serves as key and as value (a mixer that caches a latent
+    vector).  Slots with equal specs share a group: one pool, one table per request."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     block_size: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)

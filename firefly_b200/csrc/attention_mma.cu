@@ -14,6 +14,12 @@
 // Compiled once per head size: -DFF_HEAD_DIM=<multiple of 16, up to 256>.
 // Cache layout of a slot: [num_blocks][2 (k,v)][n_kv_heads][block_size][head_dim].
 #include "common.cuh"
+
+// Planes of a cache page: 2 (keys, then values) or, compiled with -DFF_KV_PLANES=1, one plane whose rows are
+// keys and values at once (a mixer that caches one vector per token and reads values from its key rows).
+#ifndef FF_KV_PLANES
+#define FF_KV_PLANES 2
+#endif
 #include <math_constants.h>
 
 #ifndef FF_HEAD_DIM
@@ -76,7 +82,7 @@ __device__ __forceinline__ long long kv_row_offset(const int* __restrict__ bt, i
         const int pi = key / block_size;
         const int page = pi < max_blocks ? bt[pi] : -1;
         if (page >= 0 && page < num_blocks)
-            off = ((((long long)page * 2) * nkv + kh) * block_size + (key - pi * block_size)) * D;
+            off = ((((long long)page * FF_KV_PLANES) * nkv + kh) * block_size + (key - pi * block_size)) * D;
         else if (status != nullptr)
             atomicExch(status, 4);
     }
@@ -281,7 +287,7 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
     const int kv_lo = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
     const int t_begin = kv_lo / BN, t_end = (kv_hi + BN - 1) / BN;
 
-    const size_t v_off = (size_t)nkv * block_size * D;
+    const size_t v_off = (size_t)(FF_KV_PLANES - 1) * nkv * block_size * D;
     __shared__ long long s_row_off[2][BN];
     kv_row_offsets(s_row_off[0], bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi, status);
     if (t_begin + 1 < t_end)
@@ -528,7 +534,7 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
         t_end = min(t1, t_begin + per);
     }
 
-    const size_t v_off = (size_t)nkv * block_size * D;
+    const size_t v_off = (size_t)(FF_KV_PLANES - 1) * nkv * block_size * D;
     __shared__ long long s_row_off[2][BN];
     if (t_begin < t_end)
         kv_row_offsets(s_row_off[0], bt, max_blocks, num_blocks, nkv, kh, block_size, t_begin * BN, kv_lo, kv_hi, hd.status);
@@ -977,6 +983,7 @@ FF_EXPORT int ff_attn_decode_heads(const void* qkv, int row_width, void* cache, 
     if (n_seqs <= 0) return 0;
     if (nkv <= 0 || nq % nkv || num_splits < 1 || status == nullptr) return FF_ERR_BAD_ARG;
     if (nq / nkv > 16 || D % 64 != 0) return FF_ERR_UNSUPPORTED;
+    if (FF_KV_PLANES != 2) return FF_ERR_UNSUPPORTED;      // it writes the newest key and value into their two planes
     FF_SMEM_LIMIT(attn_decode_heads_kernel, DECODE_SMEM);
     DecodeHeads hd{q_norm_w, k_norm_w, eps, cos_sin, max_positions, (bf16*)cache, status};
     dim3 grid(n_seqs, nkv, num_splits);
@@ -1009,6 +1016,7 @@ FF_EXPORT int ff_attn_decode_units(const void* q, int q_stride, void* cache, con
                                    int max_ranges, int finish_heads, const float* q_norm_w,
                                    const float* k_norm_w, float eps, const float* cos_sin, int max_positions,
                                    int* status, cudaStream_t stream) {
+    if (FF_KV_PLANES != 2 && finish_heads) return FF_ERR_UNSUPPORTED;
     if (n_seqs <= 0) return 0;
     if (nkv <= 0 || nq % nkv || units < n_seqs || n_seqs > NTHREADS || max_ranges < 1 || seq_ranges == nullptr)
         return FF_ERR_BAD_ARG;

@@ -16,6 +16,12 @@
 #include "common.cuh"
 #include <math_constants.h>
 
+// Planes of a cache page: 2 (keys, then values) or, compiled with -DFF_KV_PLANES=1, one plane whose rows are
+// keys and values at once (a mixer that caches one vector per token and reads values from its key rows).
+#ifndef FF_KV_PLANES
+#define FF_KV_PLANES 2
+#endif
+
 namespace ff {
 
 constexpr int ATT_WARPS = 4;
@@ -54,8 +60,8 @@ __global__ void paged_attention_simt_kernel(
             if (lane == 0) atomicExch(status, 4);
             break;
         }
-        const T* krow = cache + ((((size_t)page * 2) * nkv + kh) * block_size + j % block_size) * d;
-        const T* vrow = krow + (size_t)nkv * block_size * d;
+        const T* krow = cache + ((((size_t)page * FF_KV_PLANES) * nkv + kh) * block_size + j % block_size) * d;
+        const T* vrow = krow + (size_t)(FF_KV_PLANES - 1) * nkv * block_size * d;
         float part = 0.f;
 #pragma unroll
         for (int jj = 0; jj < ATT_PER_LANE; ++jj) {

@@ -26,6 +26,12 @@
 // Cache layout of a slot: [num_blocks][2 (k,v)][n_kv_heads][block_size][head_dim].
 #include "common.cuh"
 
+// Planes of a cache page: 2 (keys, then values) or, compiled with -DFF_KV_PLANES=1, one plane whose rows are
+// keys and values at once (a mixer that caches one vector per token and reads values from its key rows).
+#ifndef FF_KV_PLANES
+#define FF_KV_PLANES 2
+#endif
+
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <math_constants.h>
@@ -510,7 +516,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             __syncwarp();
             if (page >= 0) {
                 unsigned char* st = (kv ? Vs : Ks) + (size_t)s * KV_TILE_BYTES;
-                const int y = ((page * 2 + kv) * nkv + kh) * block_size;
+                const int y = ((page * FF_KV_PLANES + kv * (FF_KV_PLANES - 1)) * nkv + kh) * block_size;
                 tma_2d(sa(st + h * (BN * 128) + p * block_size * 128), &kv_map, h * 64, y, bar);
             }
             return true;
@@ -691,7 +697,7 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
     if (block_size < 8 || BN % block_size) return FF_ERR_UNSUPPORTED;
     if (((uintptr_t)cache & 127) || ((uintptr_t)q & 15) || (q_stride % 8) || ((uintptr_t)out & 15) || (out_stride % 8))
         return FF_ERR_UNSUPPORTED;
-    const long long rows = (long long)num_blocks * 2 * nkv * block_size;
+    const long long rows = (long long)num_blocks * FF_KV_PLANES * nkv * block_size;
     if (rows >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
     FF_SMEM_LIMIT(attn_tc_kernel, ATC_SMEM);
     CUtensorMap map;

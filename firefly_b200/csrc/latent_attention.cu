@@ -5,7 +5,8 @@
 // With q_abs[h] = W_uk[h]^T q_plain[h] (made by a batched product in front of this kernel),
 //   score(h, j) = (q_abs[h] . c_j + q_rot[h] . k_rot_j) * scale,   out_latent[h] = sum_j p_j c_j,
 // which is attention with one key/value head of size kv_rank + rot_dim whose values are the
-// cache rows themselves (the last rot_dim outputs are dropped); the head's value is then
+// cache rows themselves (the last rot_dim outputs are dropped; the cache has one plane and the
+// attention kernels are built to read values from it); the head's value is then
 // W_uv[h] out_latent[h].  This file finishes the query rows and writes the cache rows; the
 // attention itself is the paged attention the other mixers use.
 //
@@ -23,7 +24,7 @@ __global__ void latent_finish_kernel(
     const T* __restrict__ q_abs,                                          // [H, T, kv_rank]
     const float* __restrict__ c_norm_w, float eps, const double* __restrict__ freq /*[rot/2]*/,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ block_table,
-    int max_blocks, int block_size, int num_blocks, T* __restrict__ cache /*[blocks, 2, 1, block, d]*/,
+    int max_blocks, int block_size, int num_blocks, int planes, T* __restrict__ cache /*[blocks, planes, 1, block, d]*/,
     T* __restrict__ q_full /*[T, H, d]*/, int Ttot, int H, int dim, int rot, int rdims, int kv_rank,
     int* __restrict__ status) {
     pdl_prologue();
@@ -53,23 +54,26 @@ __global__ void latent_finish_kernel(
     if (page < 0 || page >= num_blocks) {
         if (threadIdx.x == 0) atomicExch(status, 2);
     } else {
-        T* krow = cache + (((size_t)page * 2) * block_size + pos % block_size) * d;
-        T* vrow = krow + (size_t)block_size * d;
+        // one plane: the row is read as key and as value; two: the value plane repeats c, with zeros behind it
+        T* krow = cache + (((size_t)page * planes) * block_size + pos % block_size) * d;
+        T* vrow = planes == 2 ? krow + (size_t)block_size * d : nullptr;
         for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) {
             const T c = from_float<T>(to_float(dkv[i]) * inv * c_norm_w[i]);
             krow[i] = c;
-            vrow[i] = c;
+            if (vrow) vrow[i] = c;
         }
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             const float a = to_float(dkv[kv_rank + i]), b = to_float(dkv[kv_rank + half + i]);
             krow[kv_rank + i] = from_float<T>(a * s_cos[i] - b * s_sin[i]);
             krow[kv_rank + half + i] = from_float<T>(b * s_cos[i] + a * s_sin[i]);
-            vrow[kv_rank + i] = from_float<T>(0.f);
-            vrow[kv_rank + half + i] = from_float<T>(0.f);
+            if (vrow) {
+                vrow[kv_rank + i] = from_float<T>(0.f);
+                vrow[kv_rank + half + i] = from_float<T>(0.f);
+            }
         }
         for (int i = threadIdx.x; i < rest; i += blockDim.x) {
             krow[kv_rank + rdims + i] = dkv[kv_rank + rdims + i];
-            vrow[kv_rank + rdims + i] = from_float<T>(0.f);
+            if (vrow) vrow[kv_rank + rdims + i] = from_float<T>(0.f);
         }
     }
     // the query rows: [q_abs | rotated part] per head
@@ -114,20 +118,21 @@ using namespace ff;
 FF_EXPORT int ff_latent_finish(const void* proj, int dtype, int proj_stride, int q_off, int dkv_off, const void* q_abs,
                                const float* c_norm_w, float eps, const double* freq, const int* positions,
                                const int* token_seq, const int* block_table, int max_blocks, int block_size,
-                               int num_blocks, void* cache, void* q_full, int T, int H, int dim, int rot, int rdims,
-                               int kv_rank, int* status, cudaStream_t stream) {
+                               int num_blocks, int planes, void* cache, void* q_full, int T, int H, int dim, int rot,
+                               int rdims, int kv_rank, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (planes != 1 && planes != 2) return FF_ERR_BAD_ARG;
     if (rot < 0 || rdims < 0 || rdims > rot || rdims % 2 || kv_rank <= 0) return FF_ERR_BAD_ARG;
     const size_t smem = (size_t)(rdims > 0 ? rdims : 2) * sizeof(float);
     if (smem > 40 * 1024) return FF_ERR_UNSUPPORTED;
     if (dtype == 0)
         FF_LAUNCH((latent_finish_kernel<float>), T, 256, smem, stream, (const float*)proj, proj_stride, q_off, dkv_off,
                   (const float*)q_abs, c_norm_w, eps, freq, positions, token_seq, block_table, max_blocks, block_size,
-                  num_blocks, (float*)cache, (float*)q_full, T, H, dim, rot, rdims, kv_rank, status);
+                  num_blocks, planes, (float*)cache, (float*)q_full, T, H, dim, rot, rdims, kv_rank, status);
     else if (dtype == 1)
         FF_LAUNCH((latent_finish_kernel<bf16>), T, 256, smem, stream, (const bf16*)proj, proj_stride, q_off, dkv_off,
                   (const bf16*)q_abs, c_norm_w, eps, freq, positions, token_seq, block_table, max_blocks, block_size,
-                  num_blocks, (bf16*)cache, (bf16*)q_full, T, H, dim, rot, rdims, kv_rank, status);
+                  num_blocks, planes, (bf16*)cache, (bf16*)q_full, T, H, dim, rot, rdims, kv_rank, status);
     else return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
     return 0;

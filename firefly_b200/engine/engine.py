@@ -161,7 +161,7 @@ class Engine:
         if not groups:
             return [], None
         es = torch.empty((), dtype=self.model.rt.dtype).element_size()
-        per_token = [len(slots) * 2 * sp.num_kv_heads * sp.head_dim * es for sp, slots, _ in groups]
+        per_token = [len(slots) * sp.planes * sp.num_kv_heads * sp.head_dim * es for sp, slots, _ in groups]
         most = opts.max_batch_size_limit * max_len
 
         def window_pages(sp, bs):

@@ -17,6 +17,9 @@ from ..config.kolorax import KoloraxConfig, file_hints
 from .registry import register_architecture
 
 DEFAULT_DECAY_RANK = 64      # rows of a wkv layer's first decay matrix when neither the configuration nor a file says
+# The design itself has no longest position (angles are formed from the position, the state has no length); the
+# engine's block tables and its cache sizing still want a bound on a request's length.
+MAX_POSITIONS = 1 << 20
 
 
 def _norm(cfg: KoloraxConfig, prefix: str) -> PartSpec:
@@ -67,7 +70,7 @@ def kolorax_spec(cfg: KoloraxConfig) -> ModelSpec:
     else:
         runs = [ScheduleEntry(i) for i in range(n)]
     return ModelSpec(
-        vocab_size=cfg.vocab, hidden_size=W, max_positions=1 << 30,
+        vocab_size=cfg.vocab, hidden_size=W, max_positions=MAX_POSITIONS,
         embedding=PartSpec("token_embedding", dict(vocab_size=cfg.vocab, hidden_size=W, scale=cfg.embedding_scale,
                                                    tensor="embed")),
         layers=tuple(layers), schedule=tuple(runs),

@@ -226,9 +226,10 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, cache: torch.Tensor, bl
     if not q.is_cuda:
         raise KernelError("firefly_b200 kernels run on a CUDA device only")
     T = out.shape[0]
-    num_blocks, two, ckv, block_size, cd = cache.shape
-    assert two == 2 and ckv == nkv and cd == d and cache.dtype == q.dtype == out.dtype
-    _check(_lib("attention_simt").ff_paged_attention_simt(
+    num_blocks, planes, ckv, block_size, cd = cache.shape
+    assert ckv == nkv and cd == d and cache.dtype == q.dtype == out.dtype
+    lib = _lib("attention_simt") if planes == 2 else _configured(load_module("attention_simt.cu", _planes_defs({}, planes)))
+    _check(lib.ff_paged_attention_simt(
         _p(q), c_int(_dt(q)), c_int(q_stride), _p(cache), _p(block_table), c_int(block_table.shape[1]),
         _p(token_seq), _p(positions), _p(out), c_int(out.shape[1]), c_int(T), c_int(nq), c_int(nkv),
         c_int(d), c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status),
@@ -447,8 +448,15 @@ def _sm_target_ctas() -> int:
     return 4 * sm_count()
 
 
-def _attn_lib(d: int) -> ctypes.CDLL:
-    return _configured(load_module("attention_mma.cu", {"FF_HEAD_DIM": d}))
+def _planes_defs(defs: dict, planes: int) -> dict:
+    """Build definitions for a cache of `planes` planes a page (2: keys and values; 1: one vector that is both)."""
+    if planes not in (1, 2):
+        raise KernelError(f"a cache page has 1 or 2 planes, got {planes}")
+    return dict(defs, FF_KV_PLANES=1) if planes == 1 else defs
+
+
+def _attn_lib(d: int, planes: int = 2) -> ctypes.CDLL:
+    return _configured(load_module("attention_mma.cu", _planes_defs({"FF_HEAD_DIM": d}, planes)))
 
 
 def mma_attention_supported(dtype: torch.dtype, d: int) -> bool:
@@ -460,8 +468,8 @@ def attn_tiled(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, o
     """Tensor-core attention for any mix of sequences (bfloat16).  ``status`` (int32 [1]) is set to 4
     when a key that must be read has no valid page in the block table."""
     _need_cuda(pages, table, cu_q, ctx_lens, out, status)
-    num_blocks, _, _, block_size, _ = pages.shape
-    _check(_attn_lib(d).ff_attn_tiled(
+    num_blocks, planes, _, block_size, _ = pages.shape
+    _check(_attn_lib(d, planes).ff_attn_tiled(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), _stream()), "attn_tiled")
@@ -472,8 +480,8 @@ def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, 
     """Split-KV tensor-core attention when every sequence has one token (bfloat16).  ``status`` as
     for `attn_tiled`."""
     _need_cuda(pages, table, cu_q, ctx_lens, out, part_o, part_ml, status)
-    num_blocks, _, _, block_size, _ = pages.shape
-    _check(_attn_lib(d).ff_attn_decode(
+    num_blocks, planes, _, block_size, _ = pages.shape
+    _check(_attn_lib(d, planes).ff_attn_decode(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(num_splits),
@@ -525,8 +533,8 @@ def attn_decode_heads(qkv, pages, table, ctx, out, nq, nkv, d, scale, window, q_
 USE_TC_ATTENTION = True     # tcgen05 attention for prompt portions where the sizes allow
 
 
-def _attn_tc_lib(d: int, page_list: Optional[int] = None) -> ctypes.CDLL:
-    defs = {"FF_HEAD_DIM": d}
+def _attn_tc_lib(d: int, page_list: Optional[int] = None, planes: int = 2) -> ctypes.CDLL:
+    defs = _planes_defs({"FF_HEAD_DIM": d}, planes)
     if page_list is not None:
         defs["FF_ATC_PAGE_LIST"] = int(page_list)       # a test build with a tiny ring of page ids
     return _configured(load_module("attention_tc.cu", defs))
@@ -546,13 +554,13 @@ def attn_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out,
     row tiles alone would leave most SMs idle); the scratch tensors are float32 with at least
     (first row + rows) * nq * count * d and ... * 2 elements."""
     _need_cuda(pages, table, cu_q, ctx_lens, out, status)
-    num_blocks, _, _, block_size, _ = pages.shape
+    num_blocks, planes, _, block_size, _ = pages.shape
     count, part_o, part_ml, row0, rows = shares if shares is not None else (1, None, None, 0, 0)
     if count > 1:
         _need_cuda(part_o, part_ml)
         need = (row0 + rows) * nq * count
         assert part_o.dtype == part_ml.dtype == torch.float32 and part_o.numel() >= need * d and part_ml.numel() >= need * 2
-    _check(_attn_tc_lib(d, page_list).ff_attn_tc(
+    _check(_attn_tc_lib(d, page_list, planes).ff_attn_tc(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), c_int(count), _p(part_o),
@@ -643,11 +651,11 @@ def attn_decode_units(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, pa
     in proportion to their lengths.  ``heads = (q_norm_w, k_norm_w, eps, cos_sin)``: q is the raw
     q|k|v projection and the kernel finishes the heads itself."""
     _need_cuda(q, pages, table, cu_q, ctx_lens, out, part_o, part_ml, seq_ranges)
-    num_blocks, _, _, block_size, _ = pages.shape
+    num_blocks, planes, _, block_size, _ = pages.shape
     assert part_o.numel() >= n_seqs * nq * units * d and part_ml.numel() >= n_seqs * nq * units * 2
     qw, kw, eps, cos_sin = heads if heads is not None else (None, None, 0.0, None)
     _need_cuda(qw, kw, cos_sin, status)
-    _check(_attn_lib(d).ff_attn_decode_units(
+    _check(_attn_lib(d, planes).ff_attn_decode_units(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), _p(seq_ranges), c_int(nq),
         c_int(nkv), c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(units),
@@ -852,15 +860,15 @@ def latent_finish(proj, q_off: int, dkv_off: int, q_abs, c_norm_w, eps: float, f
     _need_cuda(proj, q_abs, c_norm_w, freq, table, pages, q_full)
     T = proj.shape[0]
     d = kv_rank + rot
-    num_blocks, two, one, block_size, cd = pages.shape
-    assert two == 2 and one == 1 and cd == d and pages.dtype == proj.dtype == q_abs.dtype == q_full.dtype
+    num_blocks, planes, one, block_size, cd = pages.shape
+    assert planes in (1, 2) and one == 1 and cd == d and pages.dtype == proj.dtype == q_abs.dtype == q_full.dtype
     assert q_abs.shape == (heads, T, kv_rank) and q_full.shape == (T, heads * d)
     assert freq.dtype == torch.float64 and freq.numel() == rdims // 2 and c_norm_w.dtype == torch.float32
     _check(_lib("latent_attention").ff_latent_finish(
         _p(proj), c_int(_dt(proj)), c_int(proj.stride(0)), c_int(q_off), c_int(dkv_off), _p(q_abs), _p(c_norm_w),
         c_float(eps), _p(freq), _p(ctx.positions), _p(ctx.token_seq), _p(table), c_int(table.shape[1]),
-        c_int(block_size), c_int(num_blocks), _p(pages), _p(q_full), c_int(T), c_int(heads), c_int(dim), c_int(rot),
-        c_int(rdims), c_int(kv_rank), _p(ctx.status), _stream()), "latent_finish")
+        c_int(block_size), c_int(num_blocks), c_int(planes), _p(pages), _p(q_full), c_int(T), c_int(heads), c_int(dim),
+        c_int(rot), c_int(rdims), c_int(kv_rank), _p(ctx.status), _stream()), "latent_finish")
 
 
 def latent_gate(val, g, y, heads: int, vdim: int) -> None:

@@ -62,9 +62,10 @@ class LatentAttention(Part):
         self.w_in = self.w_uk = self.w_uv = self.w_o = self.c_norm = None
 
     def cache_spec(self):
-        # one key/value head per token; the value plane repeats the latent (the attention kernels read values
-        # from a plane of their own)
-        return PagedKVSpec(1, self.d, None, None if self.cache_block_size is None else int(self.cache_block_size))
+        # one vector per token in a cache of one plane: the attention kernels, built for such a cache, read it as
+        # key and as value
+        return PagedKVSpec(1, self.d, None, None if self.cache_block_size is None else int(self.cache_block_size),
+                           planes=1)
 
     def weight_specs(self) -> List[WeightSpec]:
         n, W = self.name, self.hidden
