@@ -49,14 +49,16 @@ __global__ void tanh_cast_kernel(const float* __restrict__ in, TO* __restrict__ 
 }
 
 constexpr int WKV_CHUNK = 8;     // tokens whose r, k, w are staged in shared memory at a time
-constexpr int WKV_PARTS = 4;     // threads that share a column of S: each holds a quarter of its key channels
+// threads that share a column of S, each with a share of its key channels (a block has DIM * parts threads).
+// Eight were tried up to head size 64 and were slower than four (1.30 against 1.11 ms for eight prompts of 2048).
+constexpr int wkv_parts(int dim) { return 4; }
 
 // One block per (sequence, head).  A column j of S (value channel j) is held by WKV_PARTS neighbouring
 // threads, each with DIM / WKV_PARTS key channels in registers, so a token costs DIM / WKV_PARTS steps of the
-// serial chain and two shuffles.  The bonus term's factors p_i = r_i u_i k_i are formed while a chunk is
+// serial chain and two or three shuffles.  The bonus term's factors p_i = r_i u_i k_i are formed while a chunk is
 // staged, so the inner loop has one multiply-add for it.
 //   o_j = sum_i (r_i S_ij + p_i v_j);   S_ij <- w_i S_ij + k_i v_j
-template <typename T, int DIM>
+template <typename T, int DIM, int WKV_PARTS>
 __global__ void __launch_bounds__(DIM * WKV_PARTS) wkv_scan_kernel(
     const T* __restrict__ rkvg /*[4,T,HD]*/, const float* __restrict__ dlog /*[T,HD]*/,
     const float* __restrict__ w0, const float* __restrict__ u, float* __restrict__ state, size_t state_stride,
@@ -68,8 +70,8 @@ __global__ void __launch_bounds__(DIM * WKV_PARTS) wkv_scan_kernel(
     __shared__ __align__(16) float s_r[WKV_CHUNK][DIM], s_k[WKV_CHUNK][DIM], s_w[WKV_CHUNK][DIM], s_p[WKV_CHUNK][DIM];
     __shared__ float s_v[WKV_CHUNK][DIM];
     const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-    // thread `part` of a column holds key channels 16 m + 4 part + e (m < KP / 4, e < 4): the four parts of a
-    // column then read four neighbouring 16-byte pieces of shared memory, which lie in different banks
+    // thread `part` of a column holds key channels 4 WKV_PARTS m + 4 part + e (m < KP / 4, e < 4): the parts of a
+    // column then read neighbouring 16-byte pieces of shared memory, which lie in different banks
     const int j = tid / WKV_PARTS, part = tid % WKV_PARTS;
     auto chan = [&](int i) { return (i >> 2) * (4 * WKV_PARTS) + part * 4 + (i & 3); };
     const int t0 = cu_q[s], t1 = cu_q[s + 1];
@@ -123,11 +125,15 @@ __global__ void __launch_bounds__(DIM * WKV_PARTS) wkv_scan_kernel(
         }
         __syncthreads();
         if (c0 + WKV_CHUNK < t1) fetch(c0 + WKV_CHUNK);
+        // Four partial sums shorten the chain inside a token.  (Computing all eight places of a chunk without a
+        // branch, the places past the portion's end staged as values that leave S alone, was no faster for
+        // prompts, 1.07 against 1.11 ms, and made a step of single tokens half again as slow.)  What bounds a
+        // token is the shared-memory pipe: every thread reads r, k, w and p of its sixteen channels.
 #pragma unroll
         for (int c = 0; c < WKV_CHUNK; ++c) {
             if (c < n) {
                 const float vj = s_v[c][j];
-                float acc = 0.f;
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < KP; i += 4) {
                     const int at = i * WKV_PARTS + part * 4;      // = chan(i), i a multiple of 4
@@ -135,13 +141,15 @@ __global__ void __launch_bounds__(DIM * WKV_PARTS) wkv_scan_kernel(
                     const float4 k4 = *reinterpret_cast<const float4*>(&s_k[c][at]);
                     const float4 w4 = *reinterpret_cast<const float4*>(&s_w[c][at]);
                     const float4 p4 = *reinterpret_cast<const float4*>(&s_p[c][at]);
-                    acc += r4.x * S[i] + p4.x * vj;     S[i]     = w4.x * S[i]     + k4.x * vj;
-                    acc += r4.y * S[i + 1] + p4.y * vj; S[i + 1] = w4.y * S[i + 1] + k4.y * vj;
-                    acc += r4.z * S[i + 2] + p4.z * vj; S[i + 2] = w4.z * S[i + 2] + k4.z * vj;
-                    acc += r4.w * S[i + 3] + p4.w * vj; S[i + 3] = w4.w * S[i + 3] + k4.w * vj;
+                    a0 += r4.x * S[i] + p4.x * vj;     S[i]     = w4.x * S[i]     + k4.x * vj;
+                    a1 += r4.y * S[i + 1] + p4.y * vj; S[i + 1] = w4.y * S[i + 1] + k4.y * vj;
+                    a2 += r4.z * S[i + 2] + p4.z * vj; S[i + 2] = w4.z * S[i + 2] + k4.z * vj;
+                    a3 += r4.w * S[i + 3] + p4.w * vj; S[i + 3] = w4.w * S[i + 3] + k4.w * vj;
                 }
+                float acc = (a0 + a1) + (a2 + a3);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 1);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                if (WKV_PARTS == 8) acc += __shfl_xor_sync(0xffffffffu, acc, 4);
                 if (live && part == 0) o[(size_t)(c0 + c) * HD + h * dim + j] = acc;
             }
         }
@@ -152,6 +160,7 @@ __global__ void __launch_bounds__(DIM * WKV_PARTS) wkv_scan_kernel(
     if (h == 0 && t1 > t0) {
         const T* last = x + (size_t)(t1 - 1) * W;
         for (int i = tid; i < W; i += DIM * WKV_PARTS) st[prev_off + i] = to_float(last[i]);
+        static_assert(WKV_PARTS == 4 || WKV_PARTS == 8, "the sum over a column's threads is two or three shuffles");
     }
 }
 
@@ -211,7 +220,7 @@ static int wkv_scan_launch(const void* rkvg, const float* dlog, const float* w0,
                            int dim, cudaStream_t stream) {
     dim3 grid(n_seqs, heads);
 #define FF_WKV(D)                                                                                                  \
-    FF_LAUNCH((wkv_scan_kernel<T, D>), grid, D * WKV_PARTS, 0, stream, (const T*)rkvg, dlog, w0, u, state, (size_t)state_stride, \
+    FF_LAUNCH((wkv_scan_kernel<T, D, wkv_parts(D)>), grid, D * wkv_parts(D), 0, stream, (const T*)rkvg, dlog, w0, u, state, (size_t)state_stride, \
               prev_off, (const T*)x, W, cu_q, state_slots, seq_fresh, o, Ttot, heads, dim)
     if (dim <= 32) FF_WKV(32);
     else if (dim <= 64) FF_WKV(64);

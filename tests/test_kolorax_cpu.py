@@ -93,3 +93,22 @@ def test_plain_router_keeps_to_the_best_groups():
     assert chosen == [0, 1] and abs(float(wts.sum()) - 1) < 1e-12             # 4 and 5 score higher than 1 but lie outside
     chosen, _ = P.route(z, top=2, group_count=3, group_keep=2)
     assert chosen == [0, 4]
+
+
+def test_a_cache_group_of_one_plane_keeps_one_vector_a_token():
+    from firefly_b200.cache import CacheManager, PagedKVSpec
+    from firefly_b200.models import DecoderModel, config_from_dict, spec_for
+    from firefly_b200.parts import Runtime
+    model = DecoderModel(spec_for(config_from_dict(CONFIGS["looped"])), Runtime(torch.device("cpu"), torch.float32))
+    specs = model.cache_slot_specs()
+    paged = {s: sp for s, sp in specs.items() if isinstance(sp, PagedKVSpec)}
+    assert len(paged) == 3 and all(sp.planes == 1 and sp.num_kv_heads == 1 and sp.head_dim == 40 for sp in paged.values())
+    cm = CacheManager(specs, block_size=8, num_blocks=5, max_requests=2)
+    cm.allocate_storage(torch.float32, "cpu")
+    (g,) = cm.groups
+    assert tuple(g.storage.shape) == (3, 6, 1, 1, 8, 40) and g.bytes_per_token(torch.float32) == 3 * 40 * 4
+    two = CacheManager({0: PagedKVSpec(1, 40)}, block_size=8, num_blocks=5, max_requests=2)
+    assert two.groups[0].bytes_per_token(torch.float32) == 2 * 40 * 4
+    # the recurrent runs hold state slots: every head's state in the kernel's size, and the last input row
+    states = {s: sp for s, sp in specs.items() if not isinstance(sp, PagedKVSpec)}
+    assert sorted(sp.shape[0] for sp in states.values()) == sorted([2 * 32 * 32 + 40] * 3 + [3 * 32 * 32 + 40])
