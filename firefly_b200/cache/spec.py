@@ -32,3 +32,14 @@ class StateSpec:
 
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+SUB_SLOT_STRIDE = 1 << 20
+
+
+def sub_slot(slot: int, k: int) -> int:
+    """The id of the k-th cache of a mixer that keeps several (a mixer made of mixers: its ``cache_spec()`` is a
+    tuple, one spec per inner mixer).  A run's own slot ids stay below ``SUB_SLOT_STRIDE``."""
+    if not (0 <= slot < SUB_SLOT_STRIDE):
+        raise ValueError(f"cache slot {slot} out of range")
+    return slot + (k + 1) * SUB_SLOT_STRIDE

@@ -284,7 +284,7 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
     const int first_tok = row0 / G;
     const int last_tok = min(q_len - 1, (row0 + BM - 1) / G);
     const int kv_hi = ctx + last_tok + 1;
-    const int kv_lo = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
+    const int kv_lo = first_visible_key(ctx + first_tok, window);
     const int t_begin = kv_lo / BN, t_end = (kv_hi + BN - 1) / BN;
 
     const size_t v_off = (size_t)(FF_KV_PLANES - 1) * nkv * block_size * D;
@@ -304,14 +304,14 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
         const int rg = row0 + warp * 16 + g + 8 * r;
         const int pos = ctx + min(rg, rows - 1) / G;
         hi[r] = pos + 1;
-        lo[r] = window > 0 ? max(0, pos - window + 1) : 0;
+        lo[r] = first_visible_key(pos, window);
     }
     const bool warp_active = row0 + warp * 16 < rows;
     // keys below this are visible to every row of the warp, keys at or above need the mask
     const int warp_first_pos = ctx + min(row0 + warp * 16, rows - 1) / G;
     const int warp_last_pos = ctx + min(row0 + warp * 16 + 15, rows - 1) / G;
-    const int full_lo = window > 0 ? max(0, warp_last_pos - window + 1) : 0;
-    const int warp_lo = window > 0 ? max(0, warp_first_pos - window + 1) : 0;   // first key any row sees
+    const int full_lo = first_visible_key(warp_last_pos, window);
+    const int warp_lo = first_visible_key(warp_first_pos, window);   // first key any row sees
 
     WarpState<BN> st;
     st.init();
@@ -474,7 +474,7 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
         int tiles = 0, p = 0;
         if (i < n) {
             p = ctx_lens[i];
-            tiles = (p + BN) / BN - (window > 0 ? max(0, p - window + 1) : 0) / BN;
+            tiles = (p + BN) / BN - (first_visible_key(p, window)) / BN;
         }
         int incl = tiles;
 #pragma unroll
@@ -521,7 +521,7 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
     }
     const int tok = cu_q[seq];
     const int kv_hi = pos + 1;
-    const int kv_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int kv_lo = first_visible_key(pos, window);
     const int* bt = block_table + (size_t)seq * max_blocks;
     const int t0 = kv_lo / BN, t1 = (kv_hi + BN - 1) / BN;
     int t_begin, t_end;

@@ -41,7 +41,7 @@ __global__ void paged_attention_simt_kernel(
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kh = h / (nq / nkv);
     const int seq = token_seq[t], pos = positions[t];
-    const int kv_begin = window > 0 ? max(0, pos - window + 1) : 0;
+    const int kv_begin = first_visible_key(pos, window);
     const int kv_end = pos + 1;
 
     float qr[ATT_PER_LANE], acc[ATT_PER_LANE];

@@ -296,7 +296,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         rows = q_len * G; row0 = tile * BM;
         const int first_tok = row0 / G, last_tok = min(q_len - 1, (row0 + BM - 1) / G);
         kv_hi = ctx + last_tok + 1;
-        kv_lo = window > 0 ? max(0, ctx + first_tok - window + 1) : 0;
+        kv_lo = first_visible_key(ctx + first_tok, window);
         t_begin = kv_lo / BN;
         n_tiles = (kv_hi + BN - 1) / BN - t_begin;
         if (num_splits > 1) {                    // this copy's share of the key tiles (it may be empty)
@@ -360,10 +360,10 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         // ------------------------------------------------ softmax, one thread per row --
         const int pos = ctx + token;
         const int hi = pos + 1;
-        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int lo = first_visible_key(pos, window);
         const int first_pos = ctx + row0 / G;                        // the tile's smallest position
         const int last_pos = ctx + min(q_len - 1, (row0 + BM - 1) / G);
-        const int full_lo = window > 0 ? max(0, last_pos - window + 1) : 0;
+        const int full_lo = first_visible_key(last_pos, window);
         const uint32_t lane_base = (uint32_t)((warp * 32) << 16);
         float m = -CUDART_INF_F, l = 0.f;
         bool ok = true;

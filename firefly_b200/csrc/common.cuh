@@ -110,6 +110,15 @@ __device__ __forceinline__ float ld_peer_smem(uint32_t addr, uint32_t rank) {
 
 using bf16 = __nv_bfloat16;
 
+// First key that the query at position `pos` may read.  window > 0: the last `window` keys, its own among
+// them.  window < 0: chunks of -window positions counted from position 0 of the sequence; a query reads the
+// keys of its own chunk up to itself.  0: every key from 0.  Never decreases as pos grows.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos - pos % (-window);
+    return 0;
+}
+
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(bf16 x) { return __bfloat162float(x); }
 

@@ -317,3 +317,73 @@ FF_EXPORT int ff_residual_add(float* residual, const void* delta, int delta_dtyp
     FF_LAUNCH_CHECK();
     return 0;
 }
+
+// --------------------------------------------------- norm on a part's output, added into the stream --
+// residual[t] += rms_norm(delta[t]) * w   (a block whose norms sit on the parts' outputs: the parts read the
+// stream itself), statistics and sum in 32-bit.  `copy` (optional, [T,H] in the activation type) receives the
+// updated row for the next part's products.
+namespace ff {
+template <typename TD, typename TO>
+__global__ void norm_add_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const float* __restrict__ w,
+                                float eps, TO* __restrict__ copy, int H) {
+    pdl_prologue();
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float* res = residual + (size_t)r * H;
+    const TD* dl = delta + (size_t)r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = to_float(dl[i]); ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = res[i] + to_float(dl[i]) * inv * w[i];
+        res[i] = v;
+        if (copy) copy[(size_t)r * H + i] = from_float<TO>(v);
+    }
+}
+
+// out[t,i] = act(gu[t,i]) * gu[t,I+i]; act 0: SiLU, 1: the tanh form of GELU
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int act) {
+    pdl_prologue();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = to_float(gu[t * 2 * I + i]), u = to_float(gu[t * 2 * I + I + i]);
+    float a;
+    if (act == 0) a = g / (1.0f + expf(-g));
+    else a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    out[idx] = from_float<T>(a * u);
+}
+}  // namespace ff
+
+FF_EXPORT int ff_norm_add(float* residual, const void* delta, int delta_dtype, const float* w, float eps, void* copy,
+                          int copy_dtype, int rows, int H, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H <= 0) return FF_ERR_BAD_ARG;
+    const int threads = norm_threads(H);
+    if (delta_dtype == 0 && copy_dtype == 0)
+        FF_LAUNCH((norm_add_kernel<float, float>), rows, threads, 0, stream, residual, (const float*)delta, w, eps, (float*)copy, H);
+    else if (delta_dtype == 0 && copy_dtype == 1)
+        FF_LAUNCH((norm_add_kernel<float, bf16>), rows, threads, 0, stream, residual, (const float*)delta, w, eps, (bf16*)copy, H);
+    else if (delta_dtype == 1 && copy_dtype == 1)
+        FF_LAUNCH((norm_add_kernel<bf16, bf16>), rows, threads, 0, stream, residual, (const bf16*)delta, w, eps, (bf16*)copy, H);
+    else if (delta_dtype == 1 && copy_dtype == 0)
+        FF_LAUNCH((norm_add_kernel<bf16, float>), rows, threads, 0, stream, residual, (const bf16*)delta, w, eps, (float*)copy, H);
+    else return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_glu_act(const void* gate_up, void* out, int dtype, int T, int I, int act, cudaStream_t stream) {
+    const size_t total = (size_t)T * I;
+    if (total == 0) return 0;
+    if (act != 0 && act != 1) return FF_ERR_BAD_ARG;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == 0) FF_LAUNCH((glu_act_kernel<float>), blocks, 256, 0, stream, (const float*)gate_up, (float*)out, I, total, act);
+    else if (dtype == 1) FF_LAUNCH((glu_act_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, I, total, act);
+    else return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}

@@ -20,7 +20,9 @@ namespace ff {
 
 constexpr int MOE_BM = 64, MOE_BN = 64, MOE_BK = 16;
 
-__device__ __forceinline__ float clamped_glu(float g, float u, float limit) {
+// act 1: silu(g) * u, no clamps.  act 0: the clamped form below.
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit, int act = 0) {
+    if (act == 1) return g / (1.0f + expf(-g)) * u;
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
@@ -36,69 +38,77 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
-// One warp per token.
-__global__ void moe_route_kernel(const float* __restrict__ z, int T, int E, int top, int groups, int keep,
+// One warp per token.  score 0: s = softmax(z) over all experts; 1: s = sigmoid(z).  The choice uses
+// c = s + correction (correction may be null); a group's score is its largest c (group_score 0) or the sum of
+// its two largest (1); experts of closed groups count as minus infinity (c may be negative); the weights are the
+// chosen experts' s, divided by their sum (+ 1e-20) when `renorm`.  Ties go to the lowest index.
+__global__ void moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int T, int E, int top,
+                                 int groups, int keep, int score, int group_score, int renorm,
                                  int* __restrict__ ids, float* __restrict__ wts) {
     pdl_prologue();
     extern __shared__ float sh[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= T) return;
-    float* s = sh + (size_t)warp * (2 * E + groups);
-    float* a = s + E;
+    float* s = sh + (size_t)warp * (2 * E + 2 * groups);
+    float* a = s + E;              // choice scores; minus infinity when closed or taken
     float* gs = a + E;
+    float* g_open = gs + groups;
     const float* zr = z + (size_t)t * E;
-    float mx = -CUDART_INF_F;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) { const float p = expf(zr[e] - mx); s[e] = p; sum += p; }
-    sum = warp_sum(sum);
-    __syncwarp();
-    for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+    if (score == 0) {
+        float mx = -CUDART_INF_F;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float p = expf(zr[e] - mx); s[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+    } else {
+        for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-zr[e]));
+    }
     __syncwarp();
     const int per = E / groups;
     for (int g = lane; g < groups; g += 32) {
-        float m = -1.f;
-        for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, s[e]);
-        gs[g] = m;
+        float m1 = -CUDART_INF_F, m2 = -CUDART_INF_F;
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+            const float c = s[e] + (correction ? correction[e] : 0.f);
+            if (c > m1) { m2 = m1; m1 = c; } else if (c > m2) m2 = c;
+        }
+        gs[g] = (group_score == 1 && per > 1) ? m1 + m2 : m1;
+        g_open[g] = 0.f;
     }
-    for (int e = lane; e < E; e += 32) a[e] = -1.f;
     __syncwarp();
     for (int k = 0; k < keep; ++k) {
-        float bv = -2.f;
+        float bv = -CUDART_INF_F;
         int bi = 0x7fffffff;
         for (int g = lane; g < groups; g += 32)
-            if (gs[g] > bv) { bv = gs[g]; bi = g; }
+            if (g_open[g] == 0.f && (bi == 0x7fffffff || gs[g] > bv)) { bv = gs[g]; bi = g; }
         warp_argmax(bv, bi);
-        for (int e = bi * per + lane; e < (bi + 1) * per; e += 32) a[e] = s[e];
-        if (lane == 0) gs[bi] = -3.f;
+        if (lane == 0 && bi < groups) g_open[bi] = 1.f;
         __syncwarp();
     }
+    for (int e = lane; e < E; e += 32)
+        a[e] = g_open[e / per] != 0.f ? s[e] + (correction ? correction[e] : 0.f) : -CUDART_INF_F;
+    __syncwarp();
     float total = 0.f;
-    float mine_w = 0.f;
-    int mine_id = 0;
     for (int k = 0; k < top; ++k) {
-        float bv = -2.f;
+        float bv = -CUDART_INF_F;
         int bi = 0x7fffffff;
         for (int e = lane; e < E; e += 32)
             if (a[e] > bv) { bv = a[e]; bi = e; }
         warp_argmax(bv, bi);
-        total += bv;
-        if (lane == (k & 31)) {
-            if (k < 32) { mine_w = bv; mine_id = bi; }
-        }
-        if (k >= 32 && lane == 0) { ids[(size_t)t * top + k] = bi; wts[(size_t)t * top + k] = bv; }
-        if (lane == 0) a[bi] = -4.f;
+        if (bi >= E) bi = 0;                   // cannot happen: top <= keep * per open experts with finite scores
+        const float w = s[bi];
+        total += w;
+        if (lane == 0) { ids[(size_t)t * top + k] = bi; wts[(size_t)t * top + k] = w; a[bi] = -CUDART_INF_F; }
         __syncwarp();
     }
-    const float inv = 1.0f / (total + 1e-20f);
-    if (lane < top && lane < 32) {
-        ids[(size_t)t * top + lane] = mine_id;
-        wts[(size_t)t * top + lane] = mine_w * inv;
+    if (renorm) {
+        const float inv = 1.0f / (total + 1e-20f);
+        __syncwarp();
+        for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] *= inv;
     }
-    if (top > 32 && lane == 0)
-        for (int k = 32; k < top; ++k) wts[(size_t)t * top + k] *= inv;
 }
 
 // One block: rows sorted by expert.  seg[e] .. seg[e+1] are expert e's rows; row_of[entry] is
@@ -148,7 +158,7 @@ template <typename T, bool GATEUP>
 __global__ void __launch_bounds__(256) moe_grouped_kernel(
     const T* __restrict__ a, const int* __restrict__ src_tok, const T* __restrict__ b0, const T* __restrict__ b1,
     const int* __restrict__ seg, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-    const int* __restrict__ n_tiles, void* __restrict__ out, int N, int K, float limit) {
+    const int* __restrict__ n_tiles, void* __restrict__ out, int N, int K, float limit, int act) {
     pdl_prologue();
     if ((int)blockIdx.y >= n_tiles[0]) return;
     __shared__ float As[MOE_BK][MOE_BM + 1];
@@ -201,7 +211,7 @@ __global__ void __launch_bounds__(256) moe_grouped_kernel(
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
-            if (GATEUP) ((T*)out)[(size_t)(row0 + r) * N + n] = from_float<T>(clamped_glu(acc0[i][j], acc1[i][j], limit));
+            if (GATEUP) ((T*)out)[(size_t)(row0 + r) * N + n] = from_float<T>(clamped_glu(acc0[i][j], acc1[i][j], limit, act));
             else ((float*)out)[(size_t)(row0 + r) * N + n] = acc0[i][j];
         }
     }
@@ -233,7 +243,7 @@ __global__ void __launch_bounds__(256) moe_grouped_mma_kernel(
     const bf16* __restrict__ a, const int* __restrict__ src_tok, const bf16* __restrict__ b0,
     const bf16* __restrict__ b1, const int* __restrict__ seg, const int* __restrict__ tile_expert,
     const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, void* __restrict__ out, int N, int K,
-    float limit) {
+    float limit, int act) {
     pdl_prologue();
     if ((int)blockIdx.y >= n_tiles[0]) return;
     extern __shared__ __align__(16) unsigned char mma_smem[];
@@ -330,7 +340,7 @@ __global__ void __launch_bounds__(256) moe_grouped_mma_kernel(
                     const int n = n0 + wn * 16 + nt * 8 + 2 * t4 + (c & 1);
                     if (n < N)
                         ((bf16*)out)[(size_t)(row0 + r) * N + n] =
-                            __float2bfloat16_rn(clamped_glu(acc[mt][nt][c], acc[mt][nt + 2][c], limit));
+                            __float2bfloat16_rn(clamped_glu(acc[mt][nt][c], acc[mt][nt + 2][c], limit, act));
                 }
             } else {
 #pragma unroll
@@ -375,16 +385,17 @@ using namespace ff;
 // rows of a row tile: of the tensor-core kernel (bfloat16, K % 8 == 0) or of the plain one
 FF_EXPORT int ff_moe_row_tile(int tensor_cores) { return tensor_cores ? MMA_BM : MOE_BM; }
 
-FF_EXPORT int ff_moe_route(const float* z, int T, int E, int top, int groups, int keep, int* ids, float* wts,
-                           cudaStream_t stream) {
+FF_EXPORT int ff_moe_route(const float* z, const float* correction, int T, int E, int top, int groups, int keep,
+                           int score, int group_score, int renorm, int* ids, float* wts, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
         top > keep * (E / groups))
         return FF_ERR_BAD_ARG;
     const int warps = 4;
-    const size_t smem = (size_t)warps * (2 * E + groups) * sizeof(float);
+    const size_t smem = (size_t)warps * (2 * E + 2 * groups) * sizeof(float);
     if (smem > 48 * 1024) return FF_ERR_UNSUPPORTED;
-    FF_LAUNCH(moe_route_kernel, (T + warps - 1) / warps, warps * 32, smem, stream, z, T, E, top, groups, keep, ids, wts);
+    FF_LAUNCH(moe_route_kernel, (T + warps - 1) / warps, warps * 32, smem, stream, z, correction, T, E, top, groups, keep, score,
+              group_score, renorm, ids, wts);
     FF_LAUNCH_CHECK();
     return 0;
 }
@@ -403,7 +414,7 @@ FF_EXPORT int ff_moe_plan(const int* ids, int entries, int top, int E, int row_t
 
 FF_EXPORT int ff_moe_grouped(const void* a, const int* src_tok, const void* b0, const void* b1, int dtype, int gateup,
                              const int* seg, const int* tile_expert, const int* tile_row0, const int* n_tiles,
-                             void* out, int max_tiles, int N, int K, float limit, int tensor_cores,
+                             void* out, int max_tiles, int N, int K, float limit, int act, int tensor_cores,
                              cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     if (tensor_cores) {
@@ -414,11 +425,11 @@ FF_EXPORT int ff_moe_grouped(const void* a, const int* src_tok, const void* b0, 
         if (gateup) {
             FF_SMEM_LIMIT((moe_grouped_mma_kernel<true>), MMA_SMEM);
             FF_LAUNCH((moe_grouped_mma_kernel<true>), grid, 256, MMA_SMEM, stream, (const bf16*)a, src_tok, (const bf16*)b0,
-                      (const bf16*)b1, seg, tile_expert, tile_row0, n_tiles, out, N, K, limit);
+                      (const bf16*)b1, seg, tile_expert, tile_row0, n_tiles, out, N, K, limit, act);
         } else {
             FF_SMEM_LIMIT((moe_grouped_mma_kernel<false>), MMA_SMEM);
             FF_LAUNCH((moe_grouped_mma_kernel<false>), grid, 256, MMA_SMEM, stream, (const bf16*)a, src_tok, (const bf16*)b0,
-                      (const bf16*)b1, seg, tile_expert, tile_row0, n_tiles, out, N, K, limit);
+                      (const bf16*)b1, seg, tile_expert, tile_row0, n_tiles, out, N, K, limit, act);
         }
         FF_LAUNCH_CHECK();
         return 0;
@@ -426,7 +437,7 @@ FF_EXPORT int ff_moe_grouped(const void* a, const int* src_tok, const void* b0, 
     dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
 #define FF_MOE(T, G)                                                                                               \
     FF_LAUNCH((moe_grouped_kernel<T, G>), grid, 256, 0, stream, (const T*)a, src_tok, (const T*)b0, (const T*)b1, seg, \
-              tile_expert, tile_row0, n_tiles, out, N, K, limit)
+              tile_expert, tile_row0, n_tiles, out, N, K, limit, act)
     if (dtype == 0 && gateup) FF_MOE(float, true);
     else if (dtype == 0) FF_MOE(float, false);
     else if (dtype == 1 && gateup) FF_MOE(bf16, true);

@@ -10,6 +10,7 @@ from typing import Dict, List, Mapping, Optional
 
 import torch
 
+from ..cache.spec import sub_slot
 from ..config.base import ModelSpec
 from ..parts import Runtime, build_part, part_class
 from ..parts.base import declared, host_synchronous
@@ -79,15 +80,21 @@ class DecoderModel:
     def cache_slot_specs(self) -> Dict[int, object]:
         """What each written cache slot needs (slot id -> spec)."""
         out: Dict[int, object] = {}
+        whole: Dict[int, object] = {}
         for layer, slot, write in self.schedule:
             if write:
-                out[slot] = self.blocks[layer].cache_spec()
+                spec = whole[slot] = self.blocks[layer].cache_spec()
+                if isinstance(spec, (tuple, list)):      # a mixer made of mixers: one cache per inner mixer
+                    for k, sub in enumerate(spec):
+                        out[sub_slot(slot, k)] = sub
+                else:
+                    out[slot] = spec
         for layer, slot, write in self.schedule:
             if not write:
                 want = self.blocks[layer].cache_spec()
-                if out.get(slot) != want:
+                if whole.get(slot) != want:
                     raise ValueError(f"layer {layer} reads cache slot {slot}, whose shape "
-                                     f"{out.get(slot)} is not what it needs ({want})")
+                                     f"{whole.get(slot)} is not what it needs ({want})")
         return out
 
     # -- run ------------------------------------------------------------------
@@ -95,6 +102,7 @@ class DecoderModel:
         """Logits float32 [len(ctx.logits_rows), vocab] for this step's tokens."""
         if not self.bound:
             raise RuntimeError("model has no weights bound")
+        ctx.memo.pop("stream_copy", None)      # a block's copy of the stream in the activation type belongs to one pass
         residual = self.embedding.forward(ctx)
         if self.embedding_position is not None:
             self.embedding_position.apply_to_embedding(residual, ctx)

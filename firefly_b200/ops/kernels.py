@@ -82,6 +82,8 @@ _MODULES = {
     "wkv": ("wkv.cu", None),
     "latent_attention": ("latent_attention.cu", None),
     "moe": ("moe.cu", None),
+    "ssm": ("ssm.cu", None),
+    "head_finish": ("head_finish.cu", None),
 }
 
 
@@ -898,13 +900,22 @@ def moe_row_tile(tensor_cores: bool) -> int:
     return int(_lib("moe").ff_moe_row_tile(c_int(1 if tensor_cores else 0)))
 
 
-def moe_route(z, ids, wts, groups: int, keep: int) -> None:
-    """Choice of experts per token from router logits z float32 [T,E]: ids int32 [T,top], wts float32 [T,top]."""
-    _need_cuda(z, ids, wts)
+ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1            # how router logits become scores
+GROUP_BY_BEST, GROUP_BY_TWO_BEST = 0, 1        # a group's score: its largest choice score, or the sum of its two largest
+GLU_CLAMPED_SWISH, GLU_SILU = 0, 1             # an expert's activation
+
+
+def moe_route(z, ids, wts, groups: int, keep: int, *, score: int = ROUTE_SOFTMAX, correction=None,
+              group_score: int = GROUP_BY_BEST, renormalize: bool = True) -> None:
+    """Choice of experts per token from router logits z float32 [T,E]: ids int32 [T,top], wts float32 [T,top].
+    ``correction`` float32 [E]: added to the scores for the choice only (the weights are the plain scores)."""
+    _need_cuda(z, ids, wts, correction)
     T, E = z.shape
     top = ids.shape[1]
     assert z.dtype == torch.float32 and ids.dtype == torch.int32 and wts.dtype == torch.float32 and wts.shape == ids.shape
-    _check(_lib("moe").ff_moe_route(_p(z), c_int(T), c_int(E), c_int(top), c_int(groups), c_int(keep), _p(ids), _p(wts),
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
+    _check(_lib("moe").ff_moe_route(_p(z), _p(correction), c_int(T), c_int(E), c_int(top), c_int(groups), c_int(keep),
+                                   c_int(score), c_int(group_score), c_int(1 if renormalize else 0), _p(ids), _p(wts),
                                    _stream()), "moe_route")
 
 
@@ -926,10 +937,11 @@ def moe_plan(ids, E: int, seg, row_of, src_tok, tile_expert, tile_row0, n_tiles,
                                   _stream()), "moe_plan")
 
 
-def moe_grouped(a, src_tok, b0, b1, plan, out, limit: float = 0.0, tensor_cores: bool = False) -> None:
+def moe_grouped(a, src_tok, b0, b1, plan, out, limit: float = 0.0, tensor_cores: bool = False,
+                act: int = GLU_CLAMPED_SWISH) -> None:
     """Grouped product over the experts' stacked matrices.  With ``b1`` (gate|up): rows of ``a`` [T,K] gathered
-    by src_tok, b0/b1 [E,N,K], out[row] = g * sigmoid(1.702 g) * (u + 1) with the clamps of ``limit``, in a's
-    type.  Without: a [rows,K] in place, out float32 [rows,N].  ``plan`` = (seg, tile_expert, tile_row0, n_tiles,
+    by src_tok, b0/b1 [E,N,K], out[row] = g * sigmoid(1.702 g) * (u + 1) with the clamps of ``limit``
+    (``act`` GLU_CLAMPED_SWISH) or silu(g) * u (GLU_SILU), in a's type.  Without: a [rows,K] in place, out float32 [rows,N].  ``plan`` = (seg, tile_expert, tile_row0, n_tiles,
     max_tiles), made with the same ``tensor_cores``: the mma.sync kernel (bfloat16, K % 8 == 0) or the plain one."""
     seg, tile_expert, tile_row0, n_tiles, max_tiles = plan
     _need_cuda(a, src_tok, b0, b1, out)
@@ -939,8 +951,8 @@ def moe_grouped(a, src_tok, b0, b1, plan, out, limit: float = 0.0, tensor_cores:
     assert not tensor_cores or (a.dtype == torch.bfloat16 and Kd % 8 == 0)
     _check(_lib("moe").ff_moe_grouped(_p(a), _p(src_tok), _p(b0), _p(b1), c_int(_dt(a)), c_int(1 if b1 is not None else 0),
                                      _p(seg), _p(tile_expert), _p(tile_row0), _p(n_tiles), _p(out), c_int(max_tiles),
-                                     c_int(N), c_int(Kd), c_float(limit), c_int(1 if tensor_cores else 0),
-                                     _stream()), "moe_grouped")
+                                     c_int(N), c_int(Kd), c_float(limit), c_int(act),
+                                     c_int(1 if tensor_cores else 0), _stream()), "moe_grouped")
 
 
 def clamped_glu(gu, y, limit: float) -> None:
@@ -961,3 +973,129 @@ def moe_combine(residual, rows, row_of, wts, shared, mult: float) -> None:
     assert shared is None or (shared.dtype == torch.float32 and shared.shape == residual.shape)
     _check(_lib("moe").ff_moe_combine(_p(residual), _p(rows), _p(row_of), _p(wts), _p(shared), c_float(mult), c_int(T),
                                      c_int(top), c_int(W), _stream()), "moe_combine")
+
+
+# --------------------------------------------------------------------------- #
+# norms on a part's output, gated linear units with a choice of activation
+def norm_add(residual: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float,
+             copy: Optional[torch.Tensor] = None) -> None:
+    """residual (float32 [T,H]) += rms_norm(delta) * weight, statistics and sum in 32-bit; ``copy`` [T,H]
+    (any engine type) receives the updated rows."""
+    _need_cuda(residual, delta, weight, copy)
+    T, H = residual.shape
+    assert residual.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == H
+    assert delta.shape == residual.shape and (copy is None or copy.shape == residual.shape)
+    _check(_lib("elementwise").ff_norm_add(_p(residual), _p(delta), c_int(_dt(delta)), _p(weight), c_float(eps), _p(copy),
+                                          c_int(_dt(copy) if copy is not None else 0), c_int(T), c_int(H), _stream()),
+           "norm_add")
+
+
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def glu_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out[t,i] = act(gate_up[t,i]) * gate_up[t,I+i]; act: "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    _need_cuda(gate_up, out)
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
+    _check(_lib("elementwise").ff_glu_act(_p(gate_up), _p(out), c_int(_dt(out)), c_int(T), c_int(I),
+                                         c_int(GLU_ACTIVATIONS[activation]), _stream()), "glu_act")
+
+
+def rope_unit_norm_store(qkv: torch.Tensor, nq: int, nkv: int, d: int, norm_dim: int, eps: float, freq: torch.Tensor,
+                         mag: float, ctx, block_table: Optional[torch.Tensor], cache: Optional[torch.Tensor]) -> None:
+    """Heads whose unit norm comes behind the rotation: q and k heads of ``qkv`` [T, (nq + 2 nkv) d] are turned
+    (their first 2 * len(freq) elements; cos and sin times ``mag``), divided by their root mean square over
+    ``norm_dim`` elements, q written back in place, k and v into the paged cache [blocks, 2, nkv, block, d].
+    ``nkv == 0``: q only."""
+    _need_cuda(qkv, freq, block_table, cache)
+    T, width = qkv.shape
+    assert freq.dtype == torch.float64 and width == (nq + 2 * nkv) * d
+    if nkv:
+        num_blocks, two, ckv, block_size, cd = cache.shape
+        assert two == 2 and ckv == nkv and cd == d and cache.dtype == qkv.dtype
+        max_blocks = block_table.shape[1]
+    else:
+        num_blocks = block_size = max_blocks = 1
+    _check(_lib("head_finish").ff_rope_unit_norm_store(
+        _p(qkv), c_int(_dt(qkv)), c_int(width), c_int(T), c_int(nq), c_int(nkv), c_int(d), c_int(norm_dim), c_float(eps),
+        _p(freq), c_int(2 * freq.numel()), c_float(mag), _p(ctx.positions), _p(ctx.token_seq), _p(block_table),
+        c_int(max_blocks), c_int(block_size), c_int(num_blocks), _p(cache), _p(ctx.status), _stream()),
+        "rope_unit_norm_store")
+
+
+# --------------------------------------------------------------------------- #
+# recurrences with one scalar decay per head and token (csrc/ssm.cu)
+SCAN_MAX_KEY, SCAN_MAX_VALUE = 128, 128
+
+
+def scan_state_floats(heads: int, N: int, V: int) -> int:
+    """Floats of a request's state for `heads` heads of key size N and value size V, in the recurrence
+    kernel's own layout (sizes rounded up to what the kernel is instantiated for)."""
+    if not (0 < N <= SCAN_MAX_KEY and 0 < V <= SCAN_MAX_VALUE):
+        raise KernelError(f"recurrence: key size {N} / value size {V} not supported "
+                          f"(up to {SCAN_MAX_KEY} / {SCAN_MAX_VALUE})")
+    pad = 16 if N <= 16 else (32 if N <= 32 else (64 if N <= 64 else 128))
+    threads = -(-(V * 4) // 32) * 32
+    return heads * (pad // 4) * threads
+
+
+def causal_conv_silu(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor,
+                     state: torch.Tensor, conv_off: int, ctx, out: torch.Tensor) -> None:
+    """out[t,c] = silu(bias[c] + sum_j weight[c,j] * x[t - (taps-1) + j, col0 + c]) along each sequence; the inputs
+    in front of a portion come from the request's state slot ([taps-1, channels] floats at ``conv_off``, zeros for
+    a fresh request), which is then brought up to date."""
+    _need_cuda(x, weight, bias, state, out)
+    T = x.shape[0]
+    taps = weight.shape[1]
+    assert weight.dtype == bias.dtype == state.dtype == torch.float32 and weight.shape[0] == channels == bias.numel()
+    assert out.shape == (T, channels) and out.dtype == x.dtype and state.dim() == 2
+    assert state.shape[1] >= conv_off + (taps - 1) * channels
+    _check(_lib("ssm").ff_causal_conv_silu(
+        _p(x), c_int(_dt(x)), c_int(x.stride(0)), c_int(col0), _p(weight), _p(bias), _p(state),
+        ctypes.c_longlong(state.stride(0)), c_int(conv_off), _p(ctx.token_seq), _p(ctx.cu_q), _p(ctx.state_slots),
+        _p(ctx.seq_fresh), _p(out), c_int(T), c_int(ctx.num_seqs), c_int(channels), c_int(taps), _stream()),
+        "causal_conv_silu")
+    global LAUNCHES
+    if taps > 1:
+        LAUNCHES += 1     # the kernel that saves the last inputs
+
+
+def scalar_decay_scan(q, k, v, state: torch.Tensor, state_off: int, ctx, o: torch.Tensor, heads: int, N: int, V: int, *,
+                      heads_per_group: int = 1, silu_inputs: bool = False, decay: Optional[torch.Tensor] = None,
+                      step=None, step_bias=None, a_log=None, skip=None) -> None:
+    """S = a S + b k v^T, o = S^T q (+ skip * v) per head, token by token, one block per (sequence, head).
+    ``q``, ``k``, ``v``: (matrix [T, *], first column); a q/k row holds [groups, N], a v row [heads, V].
+    Either ``decay`` float32 [heads] (a constant, b = 1) or ``step`` = (matrix, first column) with ``step_bias``,
+    ``a_log``, ``skip`` float32 [heads]: s = softplus(step + bias), a = exp(-exp(a_log) s), b = s.
+    ``state`` float32 [slots, *]: `scan_state_floats` floats from ``state_off``; o float32 [T, heads * V]."""
+    (qm, q0), (km, k0), (vm, v0) = q, k, v
+    _need_cuda(state, o, decay, step_bias, a_log, skip)
+    T = o.shape[0]
+    assert qm.dtype == km.dtype == vm.dtype and qm.stride(1) == km.stride(1) == vm.stride(1) == 1
+    assert o.dtype == torch.float32 and o.shape == (T, heads * V) and state.dtype == torch.float32
+    assert state.shape[1] >= state_off + scan_state_floats(heads, N, V)
+    mode = 0 if decay is not None else 1
+    sm, s0 = step if step is not None else (None, 0)
+    if mode == 1:
+        assert sm.dtype == qm.dtype and step_bias is not None and a_log is not None
+    _check(_lib("ssm").ff_scalar_decay_scan(
+        _p(qm), c_int(qm.stride(0)), c_int(q0), _p(km), c_int(km.stride(0)), c_int(k0), _p(vm), c_int(vm.stride(0)),
+        c_int(v0), c_int(_dt(qm)), c_int(heads_per_group), c_int(1 if silu_inputs else 0), c_int(mode), _p(decay),
+        _p(sm), c_int(sm.stride(0) if sm is not None else 0), c_int(s0), _p(step_bias), _p(a_log), _p(skip), _p(state),
+        ctypes.c_longlong(state.stride(0)), c_int(state_off), _p(ctx.cu_q), _p(ctx.state_slots), _p(ctx.seq_fresh),
+        _p(o), c_int(T), c_int(ctx.num_seqs), c_int(heads), c_int(N), c_int(V), _stream()), "scalar_decay_scan")
+
+
+def gated_rms_norm(o: torch.Tensor, gate, weight: torch.Tensor, eps: float, y: torch.Tensor, parts: int,
+                   gate_first: bool) -> None:
+    """``gate_first``: y = rms_norm(o * silu(g)) * weight, the norm over each of ``parts`` equal parts of a row;
+    else y = rms_norm(o) * weight * sigmoid(g).  o float32 [T, width]; ``gate`` = (matrix, first column)."""
+    gm, g0 = gate
+    _need_cuda(o, weight, y)
+    T, width = o.shape
+    assert o.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == width
+    assert y.shape == o.shape and y.dtype == gm.dtype and gm.stride(1) == 1
+    _check(_lib("ssm").ff_gated_rms_norm(_p(o), _p(gm), c_int(_dt(gm)), c_int(gm.stride(0)), c_int(g0), _p(weight),
+                                        c_float(eps), _p(y), c_int(T), c_int(width), c_int(parts),
+                                        c_int(0 if gate_first else 1), _stream()), "gated_rms_norm")

@@ -12,6 +12,7 @@ from typing import List, Mapping
 
 import torch
 
+from ..ops import kernels as K
 from ..weights.loader import WeightSpec
 from .base import Part, Runtime, build_part, declared, register_part
 
@@ -147,5 +148,53 @@ class ScaledPreNormBlock(Block):
         return residual, None
 
 
+class OutputNormBlock(Block):
+    """h += norm_0(mixer(h));  h += norm_1(feed_forward(h)): the norms sit on the parts' outputs and the parts
+    read the stream itself (in the activation type: a copy of the 32-bit stream that the norm kernel keeps up to
+    date; a 32-bit engine reads the stream).  A part that declares ``adds_into_residual`` adds its output into a
+    zeroed 32-bit buffer, so that what the norm reads was never rounded; another part's delta is taken as it
+    comes.  A block without a feed-forward ends after the mixer.  The norms must offer ``add_normed``."""
+
+    def __init__(self, layer_spec, rt: Runtime):
+        super().__init__(layer_spec, rt)
+        for nrm in self.norms:
+            if not hasattr(nrm, "add_normed"):
+                raise ValueError(f"arrangement '{layer_spec.arrangement}': norm '{nrm.spec.kind}' cannot norm a part's output")
+
+    def _stream_copy(self, residual, ctx):
+        if ctx.dtype == torch.float32:
+            return residual
+        x = ctx.memo.get("stream_copy")
+        if x is None:
+            x = ctx.workspace.get("stream.copy", tuple(residual.shape), ctx.dtype)
+            K.cast(residual, x)
+            ctx.memo["stream_copy"] = x
+        return x
+
+    def _delta(self, part, fuses, ctx, residual, *args):
+        if fuses:
+            delta = ctx.workspace.get("block.delta", tuple(residual.shape), torch.float32)
+            delta.zero_()
+            left = part.forward(*args, accumulate_into=delta)
+            return delta if left is None else left      # a part that could not add by itself hands its delta back
+        return part.forward(*args)
+
+    def forward(self, residual: torch.Tensor, pending, ctx, slot: int, write_cache: bool):
+        if pending is not None:                  # handed over by a block of another arrangement
+            from .norm import FoldedNorm
+            if not isinstance(pending, FoldedNorm):
+                K.residual_add(residual, pending)
+            ctx.memo.pop("stream_copy", None)
+        x = self._stream_copy(residual, ctx)
+        copy = None if x is residual else x
+        a = self._delta(self.mixer, self._mixer_fuses, ctx, residual, x, ctx, slot, write_cache)
+        self.norms[0].add_normed(residual, a, ctx, copy)
+        if self.feed_forward is not None:
+            f = self._delta(self.feed_forward, self._ffn_fuses, ctx, residual, x, ctx)
+            self.norms[1].add_normed(residual, f, ctx, copy)
+        return residual, None
+
+
 register_part("arrangement", "pre_norm", PreNormBlock)
+register_part("arrangement", "output_norm", OutputNormBlock)
 register_part("arrangement", "scaled_pre_norm", ScaledPreNormBlock)

@@ -15,7 +15,7 @@ from ..ops import kernels as K
 from ..weights.arena import FusedSpec, Piece
 from ..weights.loader import WeightSpec
 from .base import Part, register_part
-from .linear import linear_into_residual, linear_swiglu
+from .linear import apply_linear, linear_into_residual, linear_swiglu
 
 
 class SwiGLUMLP(Part):
@@ -70,4 +70,53 @@ class SwiGLUMLP(Part):
         return linear_into_residual(act, self.w_down, accumulate_into, ctx, "mlp.down", then_norm)
 
 
+class GatedMLP(Part):
+    """W_down (act(W_gate x) * (W_up x)) with the activation as a parameter ("silu" or "gelu_tanh") and the
+    tensors' leaves under the prefix as parameters (``gate_leaf``, ``up_leaf``, ``down_leaf``).  Gate and up are one
+    product against the stacked matrix [gate rows | up rows]; the activation is a kernel of its own.
+
+    Parameters: hidden_size, intermediate_size, activation."""
+
+    adds_into_residual = True        # forward(accumulate_into=...)
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.hidden = int(self.p("hidden_size"))
+        self.inter = int(self.p("intermediate_size"))
+        self.activation = str(self.p("activation", "silu"))
+        if self.activation not in K.GLU_ACTIVATIONS:
+            raise ValueError(f"{self.prefix}: activation '{self.activation}' is not one of {sorted(K.GLU_ACTIVATIONS)}")
+        self.leaves = tuple(self.p(k, d) for k, d in (("gate_leaf", "gate"), ("up_leaf", "up"), ("down_leaf", "down")))
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        g, u, d = (self.name(leaf) for leaf in self.leaves)
+        return [WeightSpec(g, (self.inter, self.hidden)), WeightSpec(u, (self.inter, self.hidden)),
+                WeightSpec(d, (self.hidden, self.inter))]
+
+    def fused_layout(self, dtype_of) -> List[FusedSpec]:
+        g, u, _ = (self.name(leaf) for leaf in self.leaves)
+        return [FusedSpec(self.name("gate_up"), (2 * self.inter, self.hidden), (Piece(g, 0), Piece(u, self.inter)))]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        g, u, d = (self.name(leaf) for leaf in self.leaves)
+        if self.name("gate_up") in tensors:
+            self.w_gate_up = self._matrix(tensors[self.name("gate_up")])
+        else:
+            a, b = self._matrix(tensors[g]), self._matrix(tensors[u])
+            if a.dtype != b.dtype:
+                a, b = a.to(torch.float32), b.to(torch.float32)
+            self.w_gate_up = torch.cat([a, b], dim=0).contiguous()
+        self.w_down = self._matrix(tensors[d])
+
+    def forward(self, x, ctx, accumulate_into=None):
+        T = x.shape[0]
+        gu = ctx.workspace.get("mlp.gate_up", (T, 2 * self.inter), ctx.dtype)
+        apply_linear(x, self.w_gate_up, gu, ctx, "mlp.gate_up")
+        act = ctx.workspace.get("mlp.act", (T, self.inter), ctx.dtype)
+        K.glu_act(gu, act, self.activation)
+        return linear_into_residual(act, self.w_down, accumulate_into, ctx, "mlp.down")
+
+
 register_part("feed_forward", "swiglu_mlp", SwiGLUMLP)
+register_part("feed_forward", "gated_mlp", GatedMLP)

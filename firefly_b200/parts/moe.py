@@ -16,6 +16,15 @@ so steps with routed experts are captured into CUDA graphs like any other.
 Parameters: hidden_size, experts, top, groups, keep, ff, limit, shared_ff (0: no shared expert),
 shared_limit.  Tensors: router [experts, W]; e<i>.gate, e<i>.up [ff, W]; e<i>.down [W, ff];
 shared.gate, shared.up [shared_ff, W]; shared.down [W, shared_ff].
+
+What the lines above fix can be chosen by further parameters (the defaults are the above):
+    score          "softmax" | "sigmoid": s = sigmoid(z), each expert by itself
+    correction     True: a tensor ``correction`` [experts] is added to s for the choice (of groups and of experts);
+                   the weights stay the plain s
+    group_score    "best" | "two_best": a group's score is the sum of its two largest choice scores
+    renormalize    False: the weights are the chosen s as they are
+    activation     "clamped_swish" | "silu": expert(x) = W_down (silu(W_gate x) * (W_up x)), no clamps, no limit
+Experts outside the open groups count as minus infinity in the choice (choice scores may be negative).
 """
 from __future__ import annotations
 
@@ -42,7 +51,13 @@ class GroupedExperts(Part):
         self.groups = int(self.p("groups", 1))
         self.keep = int(self.p("keep", self.groups))
         self.ff = int(self.p("ff"))
-        self.limit = float(self.p("limit"))
+        self.activation = {"clamped_swish": K.GLU_CLAMPED_SWISH, "silu": K.GLU_SILU}[str(self.p("activation", "clamped_swish"))]
+        self.limit = float(self.p("limit", 0.0 if self.activation == K.GLU_SILU else ...))
+        self.score = {"softmax": K.ROUTE_SOFTMAX, "sigmoid": K.ROUTE_SIGMOID}[str(self.p("score", "softmax"))]
+        self.group_score = {"best": K.GROUP_BY_BEST, "two_best": K.GROUP_BY_TWO_BEST}[str(self.p("group_score", "best"))]
+        self.renormalize = bool(self.p("renormalize", True))
+        self.has_correction = bool(self.p("correction", False))
+        self.correction = None
         self.shared_ff = int(self.p("shared_ff", 0))
         self.shared_limit = float(self.p("shared_limit", self.limit))
         if self.E % self.groups or not (0 < self.keep <= self.groups) or not (0 < self.top <= self.keep * (self.E // self.groups)):
@@ -52,6 +67,8 @@ class GroupedExperts(Part):
     def weight_specs(self) -> List[WeightSpec]:
         n, W = self.name, self.hidden
         out = [WeightSpec(n("router"), (self.E, W))]
+        if self.has_correction:
+            out.append(WeightSpec(n("correction"), (self.E,), init="zeros", as_float32=True))
         for e in range(self.E):
             out += [WeightSpec(n(f"e{e}.gate"), (self.ff, W)), WeightSpec(n(f"e{e}.up"), (self.ff, W)),
                     WeightSpec(n(f"e{e}.down"), (W, self.ff))]
@@ -82,6 +99,8 @@ class GroupedExperts(Part):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         E, W = self.E, self.hidden
         self.router = self._matrix(tensors[self.name("router")])
+        if self.has_correction:
+            self.correction = self._vector32(tensors[self.name("correction")])
         self.w_gate = self._stacked(tensors, "experts.gate", [f"e{e}.gate" for e in range(E)]).view(E, self.ff, W)
         self.w_up = self._stacked(tensors, "experts.up", [f"e{e}.up" for e in range(E)]).view(E, self.ff, W)
         self.w_down = self._stacked(tensors, "experts.down", [f"e{e}.down" for e in range(E)]).view(E, W, self.ff)
@@ -101,7 +120,8 @@ class GroupedExperts(Part):
         apply_linear(x, self.router, z, ctx, "moe.z")
         ids = ws.get("moe.ids", (T, top), torch.int32)
         wts = ws.get("moe.wts", (T, top), torch.float32)
-        K.moe_route(z, ids, wts, self.groups, self.keep)
+        K.moe_route(z, ids, wts, self.groups, self.keep, score=self.score, correction=self.correction,
+                    group_score=self.group_score, renormalize=self.renormalize)
         rows = T * top
         tc = K.moe_on_tensor_cores(dt, (W, self.ff))       # which grouped kernel runs: the plan's row tile is its
         max_tiles = K.moe_max_tiles(rows, self.E, tc)
@@ -114,7 +134,7 @@ class GroupedExperts(Part):
         K.moe_plan(ids, self.E, seg, row_of, src_tok, tile_e, tile_r, n_tiles, tc)
         plan = (seg, tile_e, tile_r, n_tiles, max_tiles)
         act = ws.get("moe.act", (rows, self.ff), dt)
-        K.moe_grouped(x, src_tok, self.w_gate, self.w_up, plan, act, self.limit, tc)
+        K.moe_grouped(x, src_tok, self.w_gate, self.w_up, plan, act, self.limit, tc, self.activation)
         outs = ws.get("moe.rows", (rows, W), torch.float32)
         K.moe_grouped(act, src_tok, self.w_down, None, plan, outs, 0.0, tc)
         shared = None

@@ -32,20 +32,32 @@ class FoldedNorm:
 
 
 class RMSNorm(Part):
+    """Parameters: size, eps; ``weight_offset`` (default 0): the multiplier is ``weight_offset + w`` (1 for a
+    weight that is stored around zero); ``tensor``: the weight's full name if it is not ``<prefix>.weight``."""
+
     foldable = True                      # fold_buffers / size / eps: the products around it can take it in
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.size = int(self.p("size"))
         self.eps = float(self.p("eps"))
+        self.weight_offset = float(self.p("weight_offset", 0.0))
+        self.tensor = self.p("tensor", None) or self.name("weight")
         self.weight: Optional[torch.Tensor] = None
         self.fold_tag = "fold.0"          # scratch of the folded form; a block gives its norms different tags
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.name("weight"), (self.size,), init="norm", as_float32=True)]
+        return [WeightSpec(self.tensor, (self.size,), init="zeros" if self.weight_offset else "norm", as_float32=True)]
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = self._vector32(tensors[self.name("weight")])
+        self.weight = self._vector32(tensors[self.tensor])
+        if self.weight_offset:
+            self.weight = (self.weight + self.weight_offset).contiguous()     # the multiplier, formed once in 32-bit
+
+    def add_normed(self, residual: torch.Tensor, delta: torch.Tensor, ctx, copy=None) -> None:
+        """residual += norm(delta): the norm sits on a part's output, the sum goes into the 32-bit stream;
+        ``copy`` receives the updated rows in its own type."""
+        K.norm_add(residual, delta, self.weight, self.eps, copy)
 
     def fold_buffers(self, T: int, ctx):
         """(xw [T, size] bfloat16, norm weight, ssq [tiles, T] float32) for a product that folds this

@@ -7,10 +7,16 @@ The reference evaluates powf/cosf/sinf per element under --use_fast_math; here
 cosines and sines come from a table computed once on the host in double
 precision and stored in 32-bit, one row per position up to ``max_positions``.
 
+``scaling`` (a parameter of ``rotary``; None: none) = dict(factor, original, fast, slow) rescales the
+frequencies in the YaRN manner: with where(n) = r ln(original / (2 pi n)) / (2 ln theta), lo = max(floor(where(fast)),
+0), hi = min(ceil(where(slow)), r - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is
+f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by ``magnitude`` = 0.1 ln(factor) + 1.
+
 ``none``: no position information (a mixer that needs none).
 """
 from __future__ import annotations
 
+import math
 from typing import Optional, Tuple
 
 import torch
@@ -36,30 +42,52 @@ class RotaryEncoding(PositionEncoding):
         if self.rotary_dim % 2 or not (0 < self.rotary_dim <= self.head_dim):
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and within the head "
                              f"({self.head_dim})")
+        sc = self.p("scaling", None)
+        self.scaling = None if not sc else tuple(float(sc[k]) for k in ("factor", "original", "fast", "slow"))
+        if self.scaling is not None and not (self.scaling[0] > 0 and self.scaling[1] > 0 and self.scaling[2] > 0
+                                             and self.scaling[3] > 0):
+            raise ValueError(f"rotary scaling {sc} must have positive factor, original, fast and slow")
+
+    @property
+    def magnitude(self) -> float:
+        """The factor on cos and sin (1 without scaling)."""
+        return 1.0 if self.scaling is None else 0.1 * math.log(self.scaling[0]) + 1.0
+
+    def _frequencies64(self) -> torch.Tensor:
+        r = self.rotary_dim
+        i = torch.arange(r // 2, dtype=torch.float64)
+        freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / r)
+        if self.scaling is None:
+            return freq
+        factor, original, fast, slow = self.scaling
+
+        def where(turns: float) -> float:
+            return r * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+        lo = max(math.floor(where(fast)), 0)
+        hi = min(math.ceil(where(slow)), r - 1)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return freq / factor * ramp + freq * (1.0 - ramp)
 
     def rotary_table(self):
-        key = ("rotary", self.rotary_dim, self.theta, self.max_positions)
+        key = ("rotary", self.rotary_dim, self.theta, self.max_positions, self.scaling)
         table = self.rt.shared.get(key)
         if table is None:
-            half = self.rotary_dim // 2
-            i = torch.arange(half, dtype=torch.float64)
-            freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.rotary_dim)
+            freq = self._frequencies64()
             ang = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * freq[None, :]
-            table = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32)
+            table = (torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1) * self.magnitude).to(torch.float32)
             table = table.contiguous().to(self.rt.device)
             self.rt.shared[key] = table
         return table, self.rotary_dim
 
 
     def frequencies(self) -> torch.Tensor:
-        """f_i = theta^(-2i/r), i in [0, r/2), as a 64-bit table on the device: for kernels that form the
-        angle position * f_i themselves (in double, so no table of positions and no longest position)."""
-        key = ("rotary_freq", self.rotary_dim, self.theta)
+        """f_i = theta^(-2i/r), i in [0, r/2) (rescaled when ``scaling`` is given), as a 64-bit table on the
+        device: for kernels that form the angle position * f_i themselves (in double, so no table of positions
+        and no longest position).  Such a kernel multiplies cos and sin by ``magnitude``."""
+        key = ("rotary_freq", self.rotary_dim, self.theta, self.scaling)
         freq = self.rt.shared.get(key)
         if freq is None:
-            i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
-            freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.rotary_dim)
-            freq = freq.contiguous().to(self.rt.device)
+            freq = self._frequencies64().contiguous().to(self.rt.device)
             self.rt.shared[key] = freq
         return freq
 
