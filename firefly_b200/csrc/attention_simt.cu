@@ -30,11 +30,13 @@ constexpr int ATT_PER_LANE = ATT_MAX_D / 32;
 
 template <typename T>
 __global__ void paged_attention_simt_kernel(
-    const T* __restrict__ q, int q_stride, const T* __restrict__ cache,
+    const T* q, int q_stride, const T* cache,
     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
     const int* __restrict__ positions, T* __restrict__ out, int out_stride, int nq, int nkv, int d,
     int block_size, int num_blocks, float scale, int window, int* __restrict__ status) {
     pdl_prologue();
+    q = pdl_fresh(q);              // the kernel in front writes the finished heads and this step's cache rows
+    cache = pdl_fresh(cache);
     __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
     __shared__ float s_acc[ATT_WARPS][ATT_MAX_D];
     const int t = blockIdx.x, h = blockIdx.y;

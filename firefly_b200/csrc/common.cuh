@@ -94,6 +94,18 @@ __device__ __forceinline__ void pdl_prologue() {
     asm volatile("griddepcontrol.launch_dependents;\n\tgriddepcontrol.wait;" ::: "memory");
 }
 
+// A pointer as the compiler may know it only behind `pdl_prologue`.  Loads through a `const __restrict__`
+// kernel argument count as invariant for the kernel's whole life and may be moved in front of
+// griddepcontrol.wait (a "memory" clobber does not hold them); a kernel that was launched early then reads
+// what the kernel in front has not written yet.  Every pointer to data that the kernel in front produces is
+// passed through this before it is read: the address is then unknown until the wait has been executed.
+template <typename P>
+__device__ __forceinline__ P* pdl_fresh(P* p) {
+    unsigned long long v = (unsigned long long)p;
+    asm volatile("" : "+l"(v));
+    return (P*)v;
+}
+
 // Barrier over all threads of all blocks of the cluster (release/acquire).
 __device__ __forceinline__ void cluster_sync_all() {
     __syncwarp();

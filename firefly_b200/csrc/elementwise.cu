@@ -169,8 +169,9 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restri
 }
 
 template <typename TI, typename TO>
-__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+__global__ void cast_kernel(const TI* in, TO* __restrict__ out, size_t n) {
     pdl_prologue();
+    in = pdl_fresh(in);
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = from_float<TO>(to_float(in[i]));
 }
@@ -324,9 +325,10 @@ FF_EXPORT int ff_residual_add(float* residual, const void* delta, int delta_dtyp
 // updated row for the next part's products.
 namespace ff {
 template <typename TD, typename TO>
-__global__ void norm_add_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const float* __restrict__ w,
+__global__ void norm_add_kernel(float* __restrict__ residual, const TD* delta, const float* __restrict__ w,
                                 float eps, TO* __restrict__ copy, int H) {
     pdl_prologue();
+    delta = pdl_fresh(delta);
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     float* res = residual + (size_t)r * H;
@@ -344,8 +346,9 @@ __global__ void norm_add_kernel(float* __restrict__ residual, const TD* __restri
 
 // out[t,i] = act(gu[t,i]) * gu[t,I+i]; act 0: SiLU, 1: the tanh form of GELU
 template <typename T>
-__global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int act) {
+__global__ void glu_act_kernel(const T* gu, T* __restrict__ out, int I, size_t total, int act) {
     pdl_prologue();
+    gu = pdl_fresh(gu);
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / I;

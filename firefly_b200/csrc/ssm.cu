@@ -23,13 +23,15 @@ __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log
 // out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1) + j, c]); inputs in front of the portion come
 // from the state slot (`conv_off`: [(taps-1), C] floats, oldest first; zeros for a fresh request).
 template <typename T>
-__global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride, int in_off,
+__global__ void causal_conv_silu_kernel(const T* in, int in_stride, int in_off,
                                         const float* __restrict__ w /*[C,taps]*/, const float* __restrict__ bias,
-                                        const float* __restrict__ state, size_t state_stride, int conv_off,
+                                        const float* state, size_t state_stride, int conv_off,
                                         const int* __restrict__ token_seq, const int* __restrict__ cu_q,
                                         const int* __restrict__ state_slots, const int* __restrict__ seq_fresh,
                                         T* __restrict__ out /*[T,C]*/, int C, int taps) {
     pdl_prologue();
+    in = pdl_fresh(in);
+    state = pdl_fresh(state);
     const int t = blockIdx.x;
     const int s = token_seq[t];
     const int t0 = cu_q[s];
@@ -54,11 +56,12 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
 // The last taps-1 inputs of every sequence, for its next step.  One thread per (sequence, channel) reads what
 // it needs of the old rows before it writes.
 template <typename T>
-__global__ void conv_state_update_kernel(const T* __restrict__ in, int in_stride, int in_off, float* __restrict__ state,
+__global__ void conv_state_update_kernel(const T* in, int in_stride, int in_off, float* __restrict__ state,
                                          size_t state_stride, int conv_off, const int* __restrict__ cu_q,
                                          const int* __restrict__ state_slots, const int* __restrict__ seq_fresh,
                                          int C, int taps) {
     pdl_prologue();
+    in = pdl_fresh(in);
     constexpr int MAX_KEEP = 15;
     const int s = blockIdx.x;
     const int t0 = cu_q[s], t1 = cu_q[s + 1];
@@ -120,9 +123,10 @@ __global__ void __launch_bounds__(512) scalar_decay_scan_kernel(
 #pragma unroll
     for (int i = 0; i < KP; ++i) S[i] = fresh ? 0.f : S_g[(size_t)i * nthr + tid];
     const int group = h / A.heads_per_group;
-    const T* qp = (const T*)A.q + A.q_off + (size_t)group * N;
-    const T* kp = (const T*)A.k + A.k_off + (size_t)group * N;
-    const T* vp = (const T*)A.v + A.v_off + (size_t)h * V;
+    const T* qp = pdl_fresh((const T*)A.q) + A.q_off + (size_t)group * N;
+    const T* kp = pdl_fresh((const T*)A.k) + A.k_off + (size_t)group * N;
+    const T* vp = pdl_fresh((const T*)A.v) + A.v_off + (size_t)h * V;
+    const T* stepp = pdl_fresh((const T*)A.step);
     float a_const = 1.f, rate = 0.f, sbias = 0.f, skip = 0.f;
     if (A.mode == 0) a_const = A.decay[h];
     else { rate = expf(A.a_log[h]); sbias = A.step_bias[h]; skip = A.skip ? A.skip[h] : 0.f; }
@@ -133,7 +137,7 @@ __global__ void __launch_bounds__(512) scalar_decay_scan_kernel(
         if (tid < SCAN_CHUNK) {
             float a = a_const, b = 1.f;
             if (A.mode == 1 && tid < n) {
-                const float raw = to_float(((const T*)A.step)[(size_t)(c0 + tid) * A.step_stride + A.step_off + h]);
+                const float raw = to_float(stepp[(size_t)(c0 + tid) * A.step_stride + A.step_off + h]);
                 const float dt = softplus_f(raw + sbias);
                 a = expf(-rate * dt);
                 b = dt;
@@ -196,10 +200,12 @@ __global__ void __launch_bounds__(512) scalar_decay_scan_kernel(
 // One block per (token, part).  order 0: y = rms(o * silu(z)) * w  (the gate in front of the norm, norm over
 // each of `parts` equal parts);  order 1: y = rms(o) * w * sigmoid(z)  (the gate behind it).
 template <typename T>
-__global__ void gated_rms_norm_kernel(const float* __restrict__ o, const T* __restrict__ z, int z_stride, int z_off,
+__global__ void gated_rms_norm_kernel(const float* o, const T* z, int z_stride, int z_off,
                                       const float* __restrict__ w, float eps, T* __restrict__ y, int width, int parts,
                                       int order) {
     pdl_prologue();
+    o = pdl_fresh(o);
+    z = pdl_fresh(z);
     __shared__ float scratch[32];
     const int t = blockIdx.x, g = blockIdx.y;
     const int per = width / parts;
