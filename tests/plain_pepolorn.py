@@ -200,3 +200,59 @@ def forward(cfg: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], laye
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
     return offset_norm(x, w["final.norm"], eps) @ w["embed"].T
+
+
+# ------------------------------------------------------------------------------------------ random weights --
+def random_weights(cfg: Mapping, seed: int) -> Dict[str, torch.Tensor]:
+    """Tensors of a model of ``cfg`` (float64, values that bfloat16 holds exactly), by name."""
+    g = torch.Generator().manual_seed(seed)
+    W = int(cfg["width"])
+
+    def rnd(*shape, std=1.0, mean=0.0):
+        return (torch.randn(*shape, generator=g, dtype=torch.float64) * std + mean).to(torch.bfloat16).double()
+
+    def lin(out, inp, gain=1.0):
+        return rnd(out, inp, std=gain / math.sqrt(inp))
+    w = {"embed": rnd(int(cfg["vocab"]), W), "final.norm": rnd(W, std=0.1)}
+    for i, L in enumerate(cfg["layers"]):
+        if L.get("weights_of") is not None:
+            continue
+        p, m = f"l{i}", L["mixer"]
+        w[p + ".norm1"] = rnd(W, std=0.1)
+        if L["type"] == "mamba2":
+            H, dv, N, G, taps = (int(m[k]) for k in ("heads", "vdim", "state", "groups", "conv"))
+            inner, C = H * dv, H * dv + 2 * G * N
+            w[p + ".mix.in"] = lin(2 * inner + 2 * G * N + H, W, 1.5)
+            w[p + ".mix.conv"] = rnd(C, taps, std=0.5)
+            w[p + ".mix.conv.b"] = rnd(C, std=0.2)
+            w[p + ".mix.dt_bias"] = rnd(H, std=0.7)
+            w[p + ".mix.A_log"] = rnd(H, std=0.6, mean=-0.5)
+            w[p + ".mix.D"] = rnd(H, std=0.3, mean=1.0)
+            w[p + ".mix.norm"] = rnd(inner, std=0.2, mean=1.0)
+            w[p + ".mix.o"] = lin(W, inner)
+        else:
+            a, b = m["left"], m["right"]
+            w[p + ".mix.left.q"] = lin(int(a["heads"]) * int(a["dim"]), W)
+            w[p + ".mix.left.k"] = lin(int(a["kv_heads"]) * int(a["dim"]), W)
+            w[p + ".mix.left.v"] = lin(int(a["kv_heads"]) * int(a["vdim"]), W)
+            w[p + ".mix.left.o"] = lin(W, int(a["heads"]) * int(a["vdim"]))
+            kq, kv = int(b["heads"]) * int(b["dim"]), int(b["heads"]) * int(b["vdim"])
+            w[p + ".mix.right.q"], w[p + ".mix.right.k"] = lin(kq, W), lin(kq, W)
+            w[p + ".mix.right.v"], w[p + ".mix.right.g"] = lin(kv, W), lin(kv, W)
+            w[p + ".mix.right.norm"] = rnd(kv, std=0.2, mean=1.0)
+            w[p + ".mix.right.o"] = lin(W, kv)
+        ml = L.get("mlp")
+        if ml is None:
+            continue
+        w[p + ".norm2"] = rnd(W, std=0.1)
+        if ml["kind"] == "dense":
+            F = int(ml["ff"])
+            w[p + ".mlp.gate"], w[p + ".mlp.up"], w[p + ".mlp.down"] = lin(F, W), lin(F, W), lin(W, F)
+        else:
+            E, F = int(ml["router"]["experts"]), int(ml["expert"]["ff"])
+            w[p + ".mlp.router"] = lin(E, W, 3.0)
+            w[p + ".mlp.correction"] = rnd(E, std=0.4, mean=-0.2)
+            for e in range(E):
+                q = f"{p}.mlp.e{e}"
+                w[q + ".gate"], w[q + ".up"], w[q + ".down"] = lin(F, W), lin(F, W), lin(W, F)
+    return w
