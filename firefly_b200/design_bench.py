@@ -1,6 +1,7 @@
-"""Throughput of the Kolorax design beside the closest existing model (Qwen3 dense) at equal size.
+"""Throughput of a design beside the closest existing model at equal size: Kolorax beside Qwen3 dense, Pepolorn
+beside Kolorax.
 
-``python bench.py --design kolorax`` calls `main` here; the default workload of bench.py is untouched.
+``python bench.py --design kolorax`` (or ``pepolorn``) calls `main` here; the default workload of bench.py is untouched.
 For each size, both models are built with seeded random weights at layer sizes that resemble a real
 model's (same width, same number of layers, the dense feed-forward as wide as the experts a token
 uses plus the shared one) and run through the engine's own loop (`Engine`: scheduler, captured decode
@@ -31,10 +32,30 @@ VOCAB = 32768
 TOP, EXPERTS, GROUPS, KEEP = 4, 16, 4, 2
 
 
+def pepolorn_config(width: int, layers: int, ff: int, shared_ff: int = 0) -> dict:
+    """Six state-space layers (inner size twice the width, heads of 64, a state of 128) around two layers of chunked
+    attention beside linear attention (heads of 128); the first layer's feed-forward dense, the others routed."""
+    moe = {"kind": "moe", "router": {"experts": EXPERTS, "top": TOP, "groups": {"count": GROUPS, "keep": KEEP}}, "expert": {"ff": ff}}
+    ssm = {"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+    heads = width // 128
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5 * 4.0,
+                 "mask": {"size": 8192}, "rot": {"base": 10000.0, "dims": 64,
+                                                 "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+        "right": {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * h / max(1, heads - 1)) for h in range(heads)]},
+        "left_scale": 1.0, "right_scale": 1.0}}
+    out = []
+    for i in range(layers):
+        L = dict(par if i % 4 == 3 else ssm)
+        L["mlp"] = {"kind": "dense", "ff": TOP * ff} if i == 0 else moe
+        out.append(L)
+    return {"architecture": "Pepolorn", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
 def kolorax_config(width: int, layers: int, ff: int, shared_ff: int) -> dict:
     heads = width // 64
     mlp = {"kind": "moe", "router": {"experts": EXPERTS, "top": TOP, "groups": {"count": GROUPS, "keep": KEEP}},
-           "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0}}
+           "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0} if shared_ff else None}
     wkv = {"type": "wkv", "mixer": {"heads": heads, "dim": 64, "decay_rank": 64}, "mlp": mlp}
     lat = {"type": "latent_attention", "mlp": mlp,
            "mixer": {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 192, "scale": 128 ** -0.5,
@@ -180,7 +201,95 @@ def kernel_table(width: int, ff: int, batch: int, prompt: int, peaks: dict) -> l
     return rows
 
 
+def pepolorn_kernel_table(width: int, ff: int, batch: int, prompt: int, peaks: dict) -> list:
+    """Pepolorn's own kernels alone against their floors, each beside the like kernel of Kolorax at equal size."""
+    from .ops import kernels as K
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    hbm = peaks["hbm_gbs"] * 1e9
+    rows = []
+
+    def add(name, us, bytes_, like=None):
+        floor = bytes_ / hbm * 1e6
+        rows.append({"kernel": name, "us": round(us, 1), "floor_us": round(floor, 2), "of_floor": round(floor / us, 3) if us else None,
+                     "bound": "memory", "like": like})
+    heads, V, N, G, taps = 2 * width // 64, 64, 128, 8, 4
+    inner, C = heads * V, heads * V + 2 * G * N
+    P_ = 2 * inner + 2 * G * N + heads
+    for label, n_seqs, q in (("prefill", batch, prompt), ("decode", batch * 8, 1)):
+        T = n_seqs * q
+        ctx = SimpleNamespace(cu_q=torch.arange(0, T + 1, q, dtype=torch.int32, device=dev), num_seqs=n_seqs,
+                              token_seq=torch.arange(T, dtype=torch.int32, device=dev) // q,
+                              positions=(torch.arange(T, dtype=torch.int32, device=dev) % q) + (0 if q > 1 else 2048),
+                              state_slots=torch.arange(1, n_seqs + 1, dtype=torch.int32, device=dev),
+                              seq_fresh=torch.zeros(n_seqs, dtype=torch.int32, device=dev),
+                              status=torch.zeros(1, dtype=torch.int32, device=dev))
+        sf = K.scan_state_floats(heads, N, V)
+        state = torch.zeros(n_seqs + 1, sf + (taps - 1) * C, dtype=torch.float32, device=dev)
+        proj = (torch.randn(T, P_, device=dev) * 0.5).to(bf)
+        xbc = torch.empty(T, C, dtype=bf, device=dev)
+        cw, cb = torch.randn(C, taps, device=dev) * 0.3, torch.zeros(C, device=dev)
+        us = _time(lambda: K.causal_conv_silu(proj, inner, C, cw, cb, state, sf, ctx, xbc), flush=flush)
+        add(f"causal_conv_silu {label} ({n_seqs} x {q})", us, T * C * 4 + 2 * n_seqs * (taps - 1) * C * 4, like="wkv_shift_mix")
+        o = torch.empty(T, inner, device=dev)
+        db, al, sk = (torch.zeros(heads, device=dev) for _ in range(3))
+        us = _time(lambda: K.scalar_decay_scan((xbc, inner + G * N), (xbc, inner), (xbc, 0), state, 0, ctx, o, heads, N, V,
+                                               heads_per_group=heads // G, step=(proj, 2 * inner + 2 * G * N), step_bias=db,
+                                               a_log=al, skip=sk), flush=flush)
+        add(f"scalar_decay_scan state-space {label} ({n_seqs} x {q})", us, T * C * 2 + T * inner * 4 + 2 * n_seqs * heads * N * V * 4, like="wkv_scan")
+        y = torch.empty(T, inner, dtype=bf, device=dev)
+        nw = torch.ones(inner, device=dev)
+        us = _time(lambda: K.gated_rms_norm(o, (proj, 0), nw, 1e-6, y, 8, True), flush=flush)
+        add(f"gated_rms_norm {label} ({T} rows)", us, T * inner * (4 + 2 + 2), like="wkv_out")
+        # linear attention: heads of 128
+        lh = width // 128
+        lproj = (torch.randn(T, 4 * lh * 128, device=dev) * 0.5).to(bf)
+        lstate = torch.zeros(n_seqs + 1, K.scan_state_floats(lh, 128, 128), dtype=torch.float32, device=dev)
+        lo = torch.empty(T, lh * 128, device=dev)
+        dec = torch.full((lh,), 0.99, device=dev)
+        us = _time(lambda: K.scalar_decay_scan((lproj, 0), (lproj, lh * 128), (lproj, 2 * lh * 128), lstate, 0, ctx, lo, lh, 128, 128,
+                                               silu_inputs=True, decay=dec), flush=flush)
+        add(f"scalar_decay_scan linear attention {label} ({n_seqs} x {q})", us, T * 3 * lh * 128 * 2 + T * lh * 128 * 4 + 2 * n_seqs * lh * 128 * 128 * 4,
+            like="wkv_scan")
+        # the like kernels of Kolorax: its recurrence (heads of 64), the five shifted mixes, its output norm
+        kh, kd = width // 64, 64
+        hd = kh * kd
+        kstate = torch.zeros(n_seqs + 1, hd * kd + width, dtype=torch.float32, device=dev)
+        rkvg = torch.randn(4, T, hd, device=dev).to(bf) * 0.1
+        dlog = torch.randn(T, hd, device=dev)
+        w0, u = torch.zeros(hd, device=dev), torch.randn(hd, device=dev)
+        x, ko = torch.randn(T, width, device=dev).to(bf), torch.empty(T, hd, device=dev)
+        us = _time(lambda: K.wkv_scan(rkvg, dlog, w0, u, kstate, hd * kd, x, ctx, ko, kh, kd), flush=flush)
+        add(f"wkv_scan {label} ({n_seqs} x {q})", us, 3 * T * hd * 2 + 2 * T * hd * 4 + 2 * n_seqs * hd * kd * 4)
+        mu, mixes = torch.rand(5, width, device=dev), torch.empty(5, T, width, dtype=bf, device=dev)
+        us = _time(lambda: K.wkv_shift_mix(x, mu, kstate, hd * kd, ctx, mixes), flush=flush)
+        add(f"wkv_shift_mix {label} ({T} rows)", us, T * width * 2 * 6)
+        ky = torch.empty(T, hd, dtype=bf, device=dev)
+        us = _time(lambda: K.wkv_out(ko, rkvg[3], torch.ones(hd, device=dev), 1e-6, ky, kh, kd), flush=flush)
+        add(f"wkv_out {label} ({T} rows)", us, T * hd * (4 + 2 + 2))
+        # the norm on a part's output beside the layer norm with the residual add
+        res, dl = torch.randn(T, width, device=dev), torch.randn(T, width, device=dev)
+        wn, bn, on = torch.ones(width, device=dev), torch.zeros(width, device=dev), torch.empty(T, width, dtype=bf, device=dev)
+        us = _time(lambda: K.norm_add(res, dl, wn, 1e-6, on), flush=flush)
+        add(f"norm_add {label} ({T} rows)", us, T * width * (4 + 4 + 4 + 2), like="add_layer_norm")
+        us = _time(lambda: K.add_layer_norm(res, dl.to(bf), wn, bn, 1e-6, on, None, 0.5), flush=flush)
+        add(f"add_layer_norm {label} ({T} rows)", us, T * width * (4 + 4 + 2 + 2))
+        # finishing the heads: rotation, unit norm, cache write
+        ah, akv, d = width // 128, max(1, width // 512), 128
+        qkv = torch.randn(T, (ah + 2 * akv) * d, device=dev).to(bf)
+        pages = torch.zeros(T // 16 + n_seqs + 2, 2, akv, 16, d, dtype=bf, device=dev)
+        per = -(-(q + 2048) // 16)
+        table = (torch.arange(n_seqs * per, dtype=torch.int32, device=dev) % (pages.shape[0] - 1) + 1).view(n_seqs, per).contiguous()
+        freq = torch.rand(32, dtype=torch.float64, device=dev)
+        us = _time(lambda: K.rope_unit_norm_store(qkv, ah, akv, d, d, 1e-6, freq, 1.2, ctx, table, pages), flush=flush)
+        add(f"rope_unit_norm_store {label} ({T} rows)", us, T * (ah + 2 * akv) * d * 2 * 2, like="qk_norm_rope_store")
+    return rows
+
+
 def main(args, peaks: dict) -> int:
+    if args.design == "pepolorn":
+        return pepolorn_main(args, peaks)
     out = {"design": "Kolorax", "beside": "Qwen3 dense at equal width, layers and feed-forward width per token",
            "dtype": args.dtype, "batch": args.batch, "prompt_len": args.prompt_len, "new_tokens": args.steps,
            "data": "synthetic token ids, seeded random weights", "peaks": peaks.get("source"), "sizes": {}}
@@ -192,5 +301,21 @@ def main(args, peaks: dict) -> int:
         dense = run_engine(qwen3_config(max_len=max_len, **size), args.dtype, args.batch, args.prompt_len, args.steps)
         out["sizes"][name] = {"shape": size, "kolorax": ours, "qwen3": dense,
                               "kernels": kernel_table(size["width"], size["ff"], args.batch, args.prompt_len, peaks)}
+    print(json.dumps(out))
+    return 0
+
+
+def pepolorn_main(args, peaks: dict) -> int:
+    out = {"design": "Pepolorn", "beside": "Kolorax at equal width, layers and experts (no shared expert)",
+           "dtype": args.dtype, "batch": args.batch, "prompt_len": args.prompt_len, "new_tokens": args.steps,
+           "data": "synthetic token ids, seeded random weights", "peaks": peaks.get("source"), "sizes": {}}
+    for name, size in SIZES.items():
+        if args.design_sizes and name not in args.design_sizes.split(","):
+            continue
+        shape = dict(size, shared_ff=0)
+        ours = run_engine(pepolorn_config(**shape), args.dtype, args.batch, args.prompt_len, args.steps)
+        beside = run_engine(kolorax_config(**shape), args.dtype, args.batch, args.prompt_len, args.steps)
+        out["sizes"][name] = {"shape": shape, "pepolorn": ours, "kolorax": beside,
+                              "kernels": pepolorn_kernel_table(size["width"], size["ff"], args.batch, args.prompt_len, peaks)}
     print(json.dumps(out))
     return 0

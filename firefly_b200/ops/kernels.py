@@ -1029,15 +1029,32 @@ def rope_unit_norm_store(qkv: torch.Tensor, nq: int, nkv: int, d: int, norm_dim:
 SCAN_MAX_KEY, SCAN_MAX_VALUE = 128, 128
 
 
-def scan_state_floats(heads: int, N: int, V: int) -> int:
-    """Floats of a request's state for `heads` heads of key size N and value size V, in the recurrence
-    kernel's own layout (sizes rounded up to what the kernel is instantiated for)."""
+def scan_plan(N: int, V: int):
+    """(key size the kernel is built for, threads that share a value column, blocks a head's columns are split
+    over, columns a block, threads a block): the recurrence kernel's layout for key size N and value size V
+    (the twin of `scan_plan` in csrc/ssm.cu; `scan_state_floats_of_kernel` is the kernel's own figure)."""
     if not (0 < N <= SCAN_MAX_KEY and 0 < V <= SCAN_MAX_VALUE):
         raise KernelError(f"recurrence: key size {N} / value size {V} not supported "
                           f"(up to {SCAN_MAX_KEY} / {SCAN_MAX_VALUE})")
     pad = 16 if N <= 16 else (32 if N <= 32 else (64 if N <= 64 else 128))
-    threads = -(-(V * 4) // 32) * 32
-    return heads * (pad // 4) * threads
+    parts = 8 if pad >= 32 else 4
+    max_cols = 512 // parts
+    vsplit = -(-V // max_cols)
+    vb = -(-V // vsplit)
+    return pad, parts, vsplit, vb, -(-(vb * parts) // 32) * 32
+
+
+def scan_state_floats(heads: int, N: int, V: int) -> int:
+    """Floats of a request's state for `heads` heads of key size N and value size V, in the recurrence
+    kernel's own layout (sizes rounded up to what the kernel is instantiated for)."""
+    pad, parts, vsplit, _, threads = scan_plan(N, V)
+    return heads * vsplit * (pad // parts) * threads
+
+
+def scan_state_floats_of_kernel(heads: int, N: int, V: int) -> int:
+    fn = _lib("ssm").ff_scan_state_floats
+    fn.restype = ctypes.c_longlong
+    return int(fn(c_int(heads), c_int(N), c_int(V)))
 
 
 def causal_conv_silu(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor,

@@ -189,7 +189,7 @@ CUTS = ([57], [20, 2, 1, 1, 30, 3], [1] * 57)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("shape", [(6, 8, 16, 3, 4, 2), (1, 40, 24, 1, 2, 1), (2, 128, 128, 2, 1, 4)])
+@pytest.mark.parametrize("shape", [(6, 8, 16, 3, 4, 2), (1, 40, 24, 1, 2, 1), (2, 128, 128, 2, 1, 4), (2, 4, 100, 1, 3, 1), (3, 64, 128, 1, 6, 3)])
 def test_state_space_mixer_alone_whole_in_portions_and_token_by_token(tmp_path, dtype, shape):
     heads, vdim, state, groups, conv, parts = shape
     layer = _with(_ssm(heads, vdim, state, groups, conv, parts), None)
@@ -387,6 +387,13 @@ def test_feed_forwards_alone(tmp_path, dtype, tokens):
             assert float(err.max()) < 2e-5, mlp["kind"]
         else:
             assert float(err.sort().values[int(0.95 * (tokens - 1))]) < 3e-2, mlp["kind"]
+
+
+def test_the_recurrence_kernels_layout_is_the_one_the_host_sizes_state_slots_for():
+    from firefly_b200.ops import kernels as K
+    for N in (1, 8, 16, 17, 32, 33, 64, 65, 100, 128):
+        for V in (1, 8, 12, 31, 32, 33, 64, 100, 128):
+            assert K.scan_state_floats(3, N, V) == K.scan_state_floats_of_kernel(3, N, V), (N, V)
 
 
 def test_norm_on_a_parts_output_alone():
