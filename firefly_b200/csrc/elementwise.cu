@@ -344,6 +344,44 @@ __global__ void norm_add_kernel(float* __restrict__ residual, const TD* delta, c
     }
 }
 
+// The same with four elements a thread and step, the row's delta and stream kept in registers between the two
+// passes (H % 4 == 0, H <= 16 * threads): one round trip to memory instead of two in a row.
+template <typename TD, typename TO>
+__global__ void norm_add_vec_kernel(float* __restrict__ residual, const TD* delta, const float* __restrict__ w,
+                                    float eps, TO* __restrict__ copy, int H) {
+    pdl_prologue();
+    delta = pdl_fresh(delta);
+    constexpr int IT = 4;
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float* res = residual + (size_t)r * H;
+    const TD* dl = delta + (size_t)r * H;
+    float4 d[IT], x[IT];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < IT; ++u) {
+        const int i = (threadIdx.x + u * blockDim.x) * 4;
+        if (i < H) {
+            d[u] = load4(dl + i);
+            x[u] = load4(res + i);
+            ss += d[u].x * d[u].x + d[u].y * d[u].y + d[u].z * d[u].z + d[u].w * d[u].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int u = 0; u < IT; ++u) {
+        const int i = (threadIdx.x + u * blockDim.x) * 4;
+        if (i < H) {
+            const float4 ww = load4(w + i);
+            const float4 v = make_float4(x[u].x + d[u].x * inv * ww.x, x[u].y + d[u].y * inv * ww.y,
+                                         x[u].z + d[u].z * inv * ww.z, x[u].w + d[u].w * inv * ww.w);
+            store4(res + i, v);
+            if (copy) store4(copy + (size_t)r * H + i, v);
+        }
+    }
+}
+
 // out[t,i] = act(gu[t,i]) * gu[t,I+i]; act 0: SiLU, 1: the tanh form of GELU
 template <typename T>
 __global__ void glu_act_kernel(const T* gu, T* __restrict__ out, int I, size_t total, int act) {
@@ -365,6 +403,23 @@ FF_EXPORT int ff_norm_add(float* residual, const void* delta, int delta_dtype, c
                           int copy_dtype, int rows, int H, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (H <= 0) return FF_ERR_BAD_ARG;
+    if (H % 4 == 0 && H <= 16 * 1024 && (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)copy | (uintptr_t)w) & 15) == 0) {
+        int threads = ((H / 4 + 3) / 4 + 31) / 32 * 32;          // four steps a thread where the row is long enough
+        if (threads < 32) threads = 32;
+        if (threads > 1024) threads = 1024;
+        while (threads * 16 < H) threads += 32;
+        if (delta_dtype == 0 && copy_dtype == 0)
+            FF_LAUNCH((norm_add_vec_kernel<float, float>), rows, threads, 0, stream, residual, (const float*)delta, w, eps, (float*)copy, H);
+        else if (delta_dtype == 0 && copy_dtype == 1)
+            FF_LAUNCH((norm_add_vec_kernel<float, bf16>), rows, threads, 0, stream, residual, (const float*)delta, w, eps, (bf16*)copy, H);
+        else if (delta_dtype == 1 && copy_dtype == 1)
+            FF_LAUNCH((norm_add_vec_kernel<bf16, bf16>), rows, threads, 0, stream, residual, (const bf16*)delta, w, eps, (bf16*)copy, H);
+        else if (delta_dtype == 1 && copy_dtype == 0)
+            FF_LAUNCH((norm_add_vec_kernel<bf16, float>), rows, threads, 0, stream, residual, (const bf16*)delta, w, eps, (float*)copy, H);
+        else return FF_ERR_BAD_ARG;
+        FF_LAUNCH_CHECK();
+        return 0;
+    }
     const int threads = norm_threads(H);
     if (delta_dtype == 0 && copy_dtype == 0)
         FF_LAUNCH((norm_add_kernel<float, float>), rows, threads, 0, stream, residual, (const float*)delta, w, eps, (float*)copy, H);

@@ -396,19 +396,20 @@ def test_the_recurrence_kernels_layout_is_the_one_the_host_sizes_state_slots_for
             assert K.scan_state_floats(3, N, V) == K.scan_state_floats_of_kernel(3, N, V), (N, V)
 
 
-def test_norm_on_a_parts_output_alone():
+@pytest.mark.parametrize("H", [40, 37, 4100, 16388])
+def test_norm_on_a_parts_output_alone(H):
     from firefly_b200.ops import kernels as K
     g = torch.Generator().manual_seed(3)
-    res, delta, w = torch.randn(11, 40, generator=g) * 3, torch.randn(11, 40, generator=g) * 5, torch.randn(40, generator=g) * 0.1
+    res, delta, w = torch.randn(11, H, generator=g) * 3, torch.randn(11, H, generator=g) * 5, torch.randn(H, generator=g) * 0.1
     want = res.double() + P.offset_norm(delta.double(), w.double(), 1e-5)
     for dt in (torch.float32, torch.bfloat16):
-        r, copy = res.cuda(), torch.empty(11, 40, dtype=dt, device="cuda")
+        r, copy = res.cuda(), torch.empty(11, H, dtype=dt, device="cuda")
         d = delta.to(dt)
         K.norm_add(r, d.cuda(), (1.0 + w).cuda(), 1e-5, copy)
         ref = res.double() + P.offset_norm(d.double(), w.double(), 1e-5)
         assert float((r.cpu().double() - ref).abs().max()) < 1e-5
         assert torch.equal(copy.cpu(), r.cpu().to(dt))
-    assert float((ref - want).abs().max()) < 0.1
+    assert float((ref - want).abs().max()) < 0.2
 
 
 # ------------------------------------------------------------------ long decoding, generation --
