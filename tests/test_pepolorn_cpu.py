@@ -76,7 +76,7 @@ def test_optional_entries_may_be_absent():
 def test_rescaled_frequencies_of_the_position_part_are_the_plain_ones():
     from firefly_b200.config.base import PartSpec
     from firefly_b200.parts import build_part
-    for rot in (ATT["rot"], {"base": 20000.0, "dims": 32, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}},
+    for rot in (ATT["rot"], {"base": 5000.0, "dims": 48, "scaling": {"factor": 16.0, "original": 512, "fast": 24.0, "slow": 2.0}},
                 {"base": 50.0, "dims": 6, "scaling": None}):
         part = build_part("position", PartSpec("rotary", dict(head_dim=64, rotary_dim=rot["dims"], theta=rot["base"],
                                                              max_positions=0, scaling=rot["scaling"])),
