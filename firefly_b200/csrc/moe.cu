@@ -42,10 +42,11 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 // c = s + correction (correction may be null); a group's score is its largest c (group_score 0) or the sum of
 // its two largest (1); experts of closed groups count as minus infinity (c may be negative); the weights are the
 // chosen experts' s, divided by their sum (+ 1e-20) when `renorm`.  Ties go to the lowest index.
-__global__ void moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int T, int E, int top,
+__global__ void moe_route_kernel(const float* z, const float* __restrict__ correction, int T, int E, int top,
                                  int groups, int keep, int score, int group_score, int renorm,
                                  int* __restrict__ ids, float* __restrict__ wts) {
     pdl_prologue();
+    z = pdl_fresh(z);
     extern __shared__ float sh[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -114,10 +115,11 @@ __global__ void moe_route_kernel(const float* __restrict__ z, const float* __res
 // One block: rows sorted by expert.  seg[e] .. seg[e+1] are expert e's rows; row_of[entry] is
 // the row of (token, choice) = entry; src_tok[row] its token; the row tiles of row_tile rows
 // (64 for the plain grouped kernel, 128 for the tensor-core one) are listed as (expert, first row) with their count in n_tiles.
-__global__ void moe_plan_kernel(const int* __restrict__ ids, int entries, int top, int E, int row_tile, int* __restrict__ seg,
+__global__ void moe_plan_kernel(const int* ids, int entries, int top, int E, int row_tile, int* __restrict__ seg,
                                 int* __restrict__ row_of, int* __restrict__ src_tok, int* __restrict__ tile_expert,
                                 int* __restrict__ tile_row0, int* __restrict__ n_tiles) {
     pdl_prologue();
+    ids = pdl_fresh(ids);
     extern __shared__ int shi[];
     int* counts = shi;
     int* offs = shi + E;
@@ -156,10 +158,12 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int entries, int to
 // out[row, n] = clamped_glu(gate, up) in type T.  Else: A = rows of `a` in place, out 32-bit.
 template <typename T, bool GATEUP>
 __global__ void __launch_bounds__(256) moe_grouped_kernel(
-    const T* __restrict__ a, const int* __restrict__ src_tok, const T* __restrict__ b0, const T* __restrict__ b1,
-    const int* __restrict__ seg, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-    const int* __restrict__ n_tiles, void* __restrict__ out, int N, int K, float limit, int act) {
+    const T* a, const int* src_tok, const T* __restrict__ b0, const T* __restrict__ b1,
+    const int* seg, const int* tile_expert, const int* tile_row0,
+    const int* n_tiles, void* __restrict__ out, int N, int K, float limit, int act) {
     pdl_prologue();
+    a = pdl_fresh(a); src_tok = pdl_fresh(src_tok); seg = pdl_fresh(seg);       // made by the kernels in front
+    tile_expert = pdl_fresh(tile_expert); tile_row0 = pdl_fresh(tile_row0); n_tiles = pdl_fresh(n_tiles);
     if ((int)blockIdx.y >= n_tiles[0]) return;
     __shared__ float As[MOE_BK][MOE_BM + 1];
     __shared__ float Bs[GATEUP ? 2 : 1][MOE_BK][MOE_BN + 1];
@@ -240,11 +244,13 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint
 
 template <bool GATEUP>
 __global__ void __launch_bounds__(256) moe_grouped_mma_kernel(
-    const bf16* __restrict__ a, const int* __restrict__ src_tok, const bf16* __restrict__ b0,
-    const bf16* __restrict__ b1, const int* __restrict__ seg, const int* __restrict__ tile_expert,
-    const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, void* __restrict__ out, int N, int K,
+    const bf16* a, const int* src_tok, const bf16* __restrict__ b0,
+    const bf16* __restrict__ b1, const int* seg, const int* tile_expert,
+    const int* tile_row0, const int* n_tiles, void* __restrict__ out, int N, int K,
     float limit, int act) {
     pdl_prologue();
+    a = pdl_fresh(a); src_tok = pdl_fresh(src_tok); seg = pdl_fresh(seg);       // made by the kernels in front
+    tile_expert = pdl_fresh(tile_expert); tile_row0 = pdl_fresh(tile_row0); n_tiles = pdl_fresh(n_tiles);
     if ((int)blockIdx.y >= n_tiles[0]) return;
     extern __shared__ __align__(16) unsigned char mma_smem[];
     typedef bf16 (*Tile)[MMA_BM][MMA_LD];                      // [stage][row][k]
@@ -354,8 +360,9 @@ __global__ void __launch_bounds__(256) moe_grouped_mma_kernel(
 
 // y[t, f] = clamped_glu(gu[t, f], gu[t, F + f])
 template <typename T>
-__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, int F, float limit, size_t total) {
+__global__ void clamped_glu_kernel(const T* gu, T* __restrict__ y, int F, float limit, size_t total) {
     pdl_prologue();
+    gu = pdl_fresh(gu);
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / F;
@@ -364,10 +371,11 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, 
 }
 
 // residual[t,:] += mult * (sum_k wts[t,k] * rows[row_of[t*top+k],:] + shared[t,:])
-__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ rows,
-                                   const int* __restrict__ row_of, const float* __restrict__ wts,
-                                   const float* __restrict__ shared, float mult, int top, int W) {
+__global__ void moe_combine_kernel(float* __restrict__ residual, const float* rows,
+                                   const int* row_of, const float* wts,
+                                   const float* shared, float mult, int top, int W) {
     pdl_prologue();
+    rows = pdl_fresh(rows); row_of = pdl_fresh(row_of); wts = pdl_fresh(wts); shared = pdl_fresh(shared);
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         float acc = 0.f;
