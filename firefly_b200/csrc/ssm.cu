@@ -180,8 +180,8 @@ constexpr int SCAN_MAX_THREADS = 512;
 // blocks of 512 threads, eight sequences of 32 heads no longer fit the GPU at once, and the prompt pass was slower.)
 struct ScanPlan { int NP, PARTS, vsplit, Vb, threads; };
 static inline bool scan_plan(int N, int V, ScanPlan* p) {
-    if (N <= 0 || N > 128 || V <= 0 || V > 128) return false;
-    p->NP = N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : 128));
+    if (N <= 0 || N > 256 || V <= 0 || V > 256) return false;
+    p->NP = N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256)));
     p->PARTS = p->NP >= 32 ? 8 : 4;
     const int max_cols = SCAN_MAX_THREADS / p->PARTS;
     p->vsplit = (V + max_cols - 1) / max_cols;
@@ -452,6 +452,7 @@ static int scan_launch(const ScanArgs& A, float* state, long long state_stride, 
         case 32: FF_SCAN(32, 8); break;
         case 64: FF_SCAN(64, 8); break;
         case 128: FF_SCAN(128, 8); break;
+        case 256: FF_SCAN(256, 8); break;
         default: return FF_ERR_UNSUPPORTED;
     }
 #undef FF_SCAN

@@ -1026,7 +1026,7 @@ def rope_unit_norm_store(qkv: torch.Tensor, nq: int, nkv: int, d: int, norm_dim:
 
 # --------------------------------------------------------------------------- #
 # recurrences with one scalar decay per head and token (csrc/ssm.cu)
-SCAN_MAX_KEY, SCAN_MAX_VALUE = 128, 128
+SCAN_MAX_KEY, SCAN_MAX_VALUE = 256, 256
 
 
 def scan_plan(N: int, V: int):
@@ -1036,7 +1036,7 @@ def scan_plan(N: int, V: int):
     if not (0 < N <= SCAN_MAX_KEY and 0 < V <= SCAN_MAX_VALUE):
         raise KernelError(f"recurrence: key size {N} / value size {V} not supported "
                           f"(up to {SCAN_MAX_KEY} / {SCAN_MAX_VALUE})")
-    pad = 16 if N <= 16 else (32 if N <= 32 else (64 if N <= 64 else 128))
+    pad = 16 if N <= 16 else (32 if N <= 32 else (64 if N <= 64 else (128 if N <= 128 else 256)))
     parts = 8 if pad >= 32 else 4
     max_cols = 512 // parts
     vsplit = -(-V // max_cols)

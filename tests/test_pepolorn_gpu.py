@@ -189,7 +189,8 @@ CUTS = ([57], [20, 2, 1, 1, 30, 3], [1] * 57)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("shape", [(6, 8, 16, 3, 4, 2), (1, 40, 24, 1, 2, 1), (2, 128, 128, 2, 1, 4), (2, 4, 100, 1, 3, 1), (3, 64, 128, 1, 6, 3)])
+@pytest.mark.parametrize("shape", [(6, 8, 16, 3, 4, 2), (1, 40, 24, 1, 2, 1), (2, 128, 128, 2, 1, 4), (2, 4, 100, 1, 3, 1), (3, 64, 128, 1, 6, 3),
+                                   (1, 160, 200, 1, 2, 1)])
 def test_state_space_mixer_alone_whole_in_portions_and_token_by_token(tmp_path, dtype, shape):
     heads, vdim, state, groups, conv, parts = shape
     layer = _with(_ssm(heads, vdim, state, groups, conv, parts), None)
@@ -205,7 +206,7 @@ def test_state_space_mixer_alone_whole_in_portions_and_token_by_token(tmp_path, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("shape", [(2, 16, 24, [0.7, 0.97]), (1, 128, 128, [0.999]), (3, 12, 20, [0.5, 1.0, 0.9])])
+@pytest.mark.parametrize("shape", [(2, 16, 24, [0.7, 0.97]), (1, 128, 128, [0.999]), (3, 12, 20, [0.5, 1.0, 0.9]), (1, 192, 256, [0.9])])
 def test_linear_attention_alone_whole_in_portions_and_token_by_token(tmp_path, dtype, shape):
     heads, dim, vdim, decay = shape
     layer = _with(_par(_att(1, 1, 16, 16, 8, 16), _lin(heads, dim, vdim, decay)), None)
@@ -391,8 +392,8 @@ def test_feed_forwards_alone(tmp_path, dtype, tokens):
 
 def test_the_recurrence_kernels_layout_is_the_one_the_host_sizes_state_slots_for():
     from firefly_b200.ops import kernels as K
-    for N in (1, 8, 16, 17, 32, 33, 64, 65, 100, 128):
-        for V in (1, 8, 12, 31, 32, 33, 64, 100, 128):
+    for N in (1, 8, 16, 17, 32, 33, 64, 65, 100, 128, 129, 256):
+        for V in (1, 8, 12, 31, 32, 33, 64, 100, 128, 130, 256):
             assert K.scan_state_floats(3, N, V) == K.scan_state_floats_of_kernel(3, N, V), (N, V)
 
 
